@@ -5,7 +5,8 @@ Cache slots (one per run-order entry that writes a cache) are grouped by what th
 keeps: (the arrays it holds per token, window).  A group has its own pool and its own block table
 per request; all slots of a group share the table (page id p means page p of every slot's
 storage in that group).  A group with a window gives pages back as soon as every position
-on them is further back than any later query can look.
+on them is further back than any later query can look; the pages of the first ``keep_first``
+positions, which every later query still sees, stay.
 
 Accounting per request, in tokens:
   extend(id, n)   make room for positions [0, n): takes pages, may raise OutOfPages
@@ -40,6 +41,7 @@ class CacheGroup:
     index: int
     key: Tuple
     window: Optional[int]
+    keep_first: int                  # with a window: the request's first positions that are never given back
     entries: Tuple                   # the CacheEntry arrays every slot of the group holds per token
     slots: List[int]                 # cache slots (run-order cache ids) stored in this group
     pool: PagePool = None            # type: ignore
@@ -85,7 +87,7 @@ class CacheManager:
             k = need.group_key()
             g = by_key.get(k)
             if g is None:
-                g = CacheGroup(len(self.groups), k, need.window, need.entries, [])
+                g = CacheGroup(len(self.groups), k, need.window, need.keep_first if need.window else 0, need.entries, [])
                 n = num_pages[k] if isinstance(num_pages, dict) else num_pages
                 g.pool = PagePool(n)
                 by_key[k] = g
@@ -107,6 +109,10 @@ class CacheManager:
             return 0
         first_pos = committed - g.window + 1   # oldest key the next query (at `committed`) sees
         return max(0, first_pos) // self.page_size
+
+    def _kept_pages(self, g: CacheGroup) -> int:
+        """Leading logical pages that hold one of the first positions a window never drops."""
+        return -(-g.keep_first // self.page_size) if g.window is not None else 0
 
     def pages_to_extend(self, rid: Optional[Hashable], n_tokens: int) -> Dict[int, int]:
         """Pages each group must give so that positions [0, n_tokens) of the request are held."""
@@ -139,7 +145,7 @@ class CacheManager:
                 out[g.index] = n_logical
             else:
                 span = min(n_tokens, max_portion) + g.window - 1
-                out[g.index] = min(n_logical, -(-span // self.page_size) + 1)
+                out[g.index] = min(n_logical, -(-span // self.page_size) + 1 + self._kept_pages(g))
         return out
 
     def fits_at_all(self, n_tokens: int, max_portion: int) -> bool:
@@ -199,10 +205,11 @@ class CacheManager:
                 continue
             table = rc.tables[g.index]
             first = min(self._first_needed_page(g, n_tokens), len(table))
-            gone = [p for p in table[:first] if p != NO_PAGE]
+            kept = self._kept_pages(g)
+            gone = [p for p in table[kept:first] if p != NO_PAGE]
             if gone:
                 g.pool.free(gone, (rid, g.index))
-                for i in range(first):
+                for i in range(kept, first):
                     table[i] = NO_PAGE
 
     def release(self, rid: Hashable) -> None:

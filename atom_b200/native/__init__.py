@@ -84,6 +84,18 @@ _SIGNATURES = {
     "atom_gelu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "atom_gemm_f32_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _vp],
     "atom_gemm_bf16_batched": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp],
+    "atom_relu2": [_vp, _i, _i64, _vp],
+    "atom_conv_rope_write": [_vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i,
+                             _i, _vp, _vp, _i64, _vp, _vp],
+    "atom_conv_state_update": [_vp, _vp, _i, _i64, _i, _i, _vp, _vp, _i, _vp],
+    "atom_window_attention": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp],
+    "atom_lightning_supports": [_i, _i],
+    "atom_lightning_scan": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "atom_lightning_gate_norm": [_vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _f, _vp, _vp],
+    "atom_moe_route": [_vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
+    "atom_moe_place": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "atom_moe_gemm": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "atom_moe_combine": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i64, _i, _i, _vp, _vp],
     "atom_rmsnorm": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "atom_qknorm_rope_kvwrite": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i, _vp, _vp,
@@ -751,6 +763,183 @@ def gelu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype
     _check(lib().atom_gelu_mul(out.data_ptr(), gate_up.data_ptr(), dtype_code(out.dtype), T, I, _stream()), "gelu_mul")
+
+
+def relu2_(x: torch.Tensor) -> None:
+    """x = relu(x)^2 in place."""
+    _cuda(x)
+    assert x.is_contiguous()
+    _check(lib().atom_relu2(x.data_ptr(), dtype_code(x.dtype), x.numel(), _stream()), "relu2")
+
+
+def conv_rope_write(q_out: torch.Tensor, qkv: torch.Tensor, H: int, G: int, dk: int, dv: int,
+                    conv_w: Optional[torch.Tensor], conv_state: Optional[torch.Tensor], freq: Optional[torch.Tensor],
+                    rot_dims: int, positions: torch.Tensor, seq_of_token: torch.Tensor, cu_q: torch.Tensor,
+                    state_slots: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], status: torch.Tensor) -> None:
+    """Per token of the packed projection [q (H dk) | k (G dk) | v (G dv)]: the short causal convolution over time on
+    every channel (conv_w [C, taps]; rows before the step from conv_state [slots, taps - 1, C], which is only read),
+    rotation of the first rot_dims numbers of every query and key head by position * freq, queries to q_out
+    [T, H dk], keys and values to their pages (csrc/window_attention.cu).  conv_w None: no convolution."""
+    _cuda(q_out, qkv, conv_w, conv_state, freq, positions, seq_of_token, cu_q, state_slots, block_table, k_pages,
+          v_pages, status)
+    T = qkv.shape[0]
+    C = (H + G) * dk + G * dv
+    taps = 0 if conv_w is None else conv_w.shape[1]
+    assert qkv.stride(1) == 1 and qkv.shape[1] >= C and q_out.is_contiguous() and q_out.shape == (T, H * dk)
+    assert q_out.dtype == qkv.dtype and block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert conv_w is None or (tuple(conv_w.shape) == (C, taps) and conv_w.is_contiguous())
+    assert taps <= 1 or (conv_state is not None and conv_state.is_contiguous() and conv_state.dtype == qkv.dtype
+                         and tuple(conv_state.shape[1:]) == (taps - 1, C))
+    assert rot_dims == 0 or (freq is not None and freq.dtype == torch.float32 and freq.numel() >= rot_dims // 2)
+    if k_pages is not None:
+        assert tuple(k_pages.shape[1:]) == (G, page_size, dk) and tuple(v_pages.shape[1:]) == (G, page_size, dv)
+        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype == qkv.dtype
+    _check(lib().atom_conv_rope_write(
+        q_out.data_ptr(), qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), T, H, G, dk, dv, _ptr(conv_w),
+        dtype_code(conv_w.dtype) if conv_w is not None else F32, taps, _ptr(conv_state) if taps > 1 else None,
+        _ptr(freq), rot_dims, positions.data_ptr(), seq_of_token.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
+        k_pages.shape[0] if k_pages is not None else 0, status.data_ptr(), _stream()), "conv_rope_write")
+
+
+def conv_state_update(conv_state: torch.Tensor, qkv: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
+                      num_seqs: int) -> None:
+    """conv_state [slots, taps - 1, C] <- every request's last taps - 1 rows of (what it held, then the step's rows)."""
+    _cuda(conv_state, qkv, cu_q, state_slots)
+    taps, C = conv_state.shape[1] + 1, conv_state.shape[2]
+    assert conv_state.is_contiguous() and qkv.stride(1) == 1 and qkv.shape[1] >= C and qkv.dtype == conv_state.dtype
+    _check(lib().atom_conv_state_update(conv_state.data_ptr(), qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), C,
+                                        taps, cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, _stream()),
+           "conv_state_update")
+
+
+def window_attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, nh: int, nkv: int,
+                     dk: int, dv: int, scale: float, softcap: float = 0.0, window: int = 0, keep_first: int = 0) -> None:
+    """Causal paged attention, key j seen from position p if j <= p and (p - j < window or j < keep_first); scores
+    scale * q.k, then softcap * tanh(score / softcap) if softcap > 0.  q [T, nh dk], out [T, nh dv], any sizes, both
+    precisions (csrc/window_attention.cu)."""
+    _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token)
+    T = q.shape[0]
+    page_size = k_pages.shape[2]
+    assert q.is_contiguous() and out.is_contiguous() and q.shape == (T, nh * dk) and out.shape == (T, nh * dv)
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, dk) and tuple(v_pages.shape[1:]) == (nkv, page_size, dv)
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    _check(lib().atom_window_attention(
+        out.data_ptr(), q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(), seq_of_token.data_ptr(), T, nh,
+        nkv, dk, dv, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first), _stream()),
+        "window_attention")
+
+
+def lightning_supports(dk: int, dv: int) -> bool:
+    return bool(lib().atom_lightning_supports(dk, dv))
+
+
+LIGHTNING_RUN = 64        # rows per run of the lightning scan in steps of more rows than this
+
+
+def lightning_run(T: int) -> int:
+    """Rows per run for a step of T rows (0: every request is walked once)."""
+    if T <= LIGHTNING_RUN:
+        return 0
+    return LIGHTNING_RUN if T <= 64 * LIGHTNING_RUN else -(-T // 64)
+
+
+def lightning_scratch_elems(T: int, num_seqs: int, H: int, dk: int, dv: int) -> int:
+    run = lightning_run(T)
+    return 1 if run == 0 else (-(-T // run) + num_seqs) * H * dk * dv
+
+
+def lightning_scan(out: torch.Tensor, proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                   scratch: Optional[torch.Tensor], cu_q: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
+                   H: int, dk: int, dv: int, write_state: bool = True) -> None:
+    """out[t] (float32 [T, H dv]) = S_t^T silu(q_t) with S_t = decay_h S_(t-1) + silu(k_t) silu(v_t)^T per head, over
+    every request's rows; proj rows are [q (H dk) | k (H dk) | v (H dv) | ...]; state [slots, H, dk, dv] float32."""
+    _cuda(out, proj, decay, state, scratch, cu_q, state_slots)
+    T = proj.shape[0]
+    run = lightning_run(T)
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, H * dv) and proj.stride(1) == 1
+    assert proj.shape[1] >= 2 * H * dk + H * dv and decay.dtype == torch.float32 and decay.numel() == H
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv)
+    assert run == 0 or (scratch is not None and scratch.dtype == torch.float32
+                        and scratch.numel() >= lightning_scratch_elems(T, num_seqs, H, dk, dv))
+    _check(lib().atom_lightning_scan(out.data_ptr(), proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0),
+                                     decay.data_ptr(), state.data_ptr(), _ptr(scratch) if run else None,
+                                     cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, T, H, dk, dv, run,
+                                     int(write_state), _stream()), "lightning_scan")
+    if run:
+        add_launches(2)      # (the runs' sums, the prefix over the runs, the outputs)
+
+
+def lightning_gate_norm(y: torch.Tensor, o: torch.Tensor, g: torch.Tensor, w: torch.Tensor, eps: float,
+                        seq_of_token: torch.Tensor) -> None:
+    """y = o / rms(o over the whole row) * w * sigmoid(g); o float32 [T, n], g a view of n columns of the projection."""
+    _cuda(y, o, g, w, seq_of_token)
+    T, n = o.shape
+    assert o.dtype == torch.float32 and o.is_contiguous() and y.is_contiguous() and y.shape == (T, n)
+    assert g.shape == (T, n) and g.stride(1) == 1 and g.dtype == y.dtype and w.numel() == n and w.is_contiguous()
+    _check(lib().atom_lightning_gate_norm(y.data_ptr(), o.data_ptr(), g.data_ptr(), dtype_code(y.dtype), g.stride(0),
+                                          w.data_ptr(), dtype_code(w.dtype), T, n, float(eps), seq_of_token.data_ptr(),
+                                          _stream()), "lightning_gate_norm")
+
+
+def moe_route(logits: torch.Tensor, E: int, top: int, score: str, renormalize: bool, seq_of_token: torch.Tensor,
+              ids: torch.Tensor, wts: torch.Tensor, counts: torch.Tensor) -> None:
+    """Per row: the ``top`` experts with the largest scores (sigmoid or softmax of logits[:, :E], float32), their
+    scores as weights (divided by their sum if renormalize), and the experts' row counts added to ``counts``."""
+    _cuda(logits, seq_of_token, ids, wts, counts)
+    T = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= E
+    assert ids.dtype == counts.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous()
+    assert wts.is_contiguous() and ids.shape == wts.shape == (T, top) and counts.numel() >= E
+    _check(lib().atom_moe_route(logits.data_ptr(), logits.stride(0), T, E, top, int(score == "softmax"),
+                                int(renormalize), seq_of_token.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                                counts.data_ptr(), _stream()), "moe_route")
+
+
+def moe_place(ids: torch.Tensor, wts: torch.Tensor, E: int, counts: torch.Tensor, offsets: torch.Tensor,
+              row_token: torch.Tensor, row_w: torch.Tensor, pair_pos: torch.Tensor) -> None:
+    """Sorts the (row, choice) pairs by expert: offsets [E + 1] (first place of every expert), for every place the
+    row it came from and its weight, for every pair its place.  ``counts`` goes back to zero."""
+    _cuda(ids, wts, counts, offsets, row_token, row_w, pair_pos)
+    pairs, top = ids.numel(), ids.shape[1]
+    assert offsets.numel() >= E + 1 and row_token.numel() >= pairs and row_w.numel() >= pairs and pair_pos.numel() >= pairs
+    assert offsets.dtype == row_token.dtype == pair_pos.dtype == torch.int32 and row_w.dtype == torch.float32
+    _check(lib().atom_moe_place(ids.data_ptr(), wts.data_ptr(), pairs, top, E, counts.data_ptr(), offsets.data_ptr(),
+                                row_token.data_ptr(), row_w.data_ptr(), pair_pos.data_ptr(), _stream()), "moe_place")
+
+
+def moe_gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, gated: bool = False,
+             row_token: Optional[torch.Tensor] = None, row_w: Optional[torch.Tensor] = None) -> None:
+    """out[r] = A[r] w[e]^T for the places r of every expert e (offsets [E + 1]); w [E, N or 2 N, K].  With row_token
+    and row_w, A[r] = row_w[r] * a[row_token[r]] (rows picked from the step's rows, weighted on the way in); else
+    A = a by place.  gated: w[e] = [gate ; up], out = silu(gate) * up."""
+    _cuda(out, a, w, offsets, row_token, row_w)
+    R, N = out.shape
+    E, K = w.shape[0], w.shape[2]
+    assert w.shape[1] == (2 * N if gated else N) and w.is_contiguous() and out.is_contiguous() and a.stride(1) == 1
+    assert a.shape[1] == K and out.dtype == a.dtype == w.dtype and (row_token is not None or a.shape[0] >= R)
+    _check(lib().atom_moe_gemm(out.data_ptr(), a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(),
+                               offsets.data_ptr(), _ptr(row_token), _ptr(row_w), R, E, N, K, int(gated),
+                               int(row_token is not None), _stream()), "moe_gemm")
+
+
+def moe_combine(out: torch.Tensor, y: torch.Tensor, pair_pos: torch.Tensor, top: int,
+                pair_w: Optional[torch.Tensor], shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                seq_of_token: torch.Tensor) -> None:
+    """out[t] = sum over t's choices k of (pair_w[t, k] *) y[pair_pos[t, k]] (+ sigmoid(gate[t]) * shared[t]);
+    gate: a float32 column view (one logit per row) or None (the shared part is added as it is)."""
+    _cuda(out, y, pair_pos, pair_w, shared, gate, seq_of_token)
+    T, n = out.shape
+    assert out.is_contiguous() and y.is_contiguous() and y.shape[1] == n and out.dtype == y.dtype
+    assert shared is None or (shared.is_contiguous() and shared.shape == (T, n) and shared.dtype == out.dtype)
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == T)
+    _check(lib().atom_moe_combine(out.data_ptr(), y.data_ptr(), dtype_code(out.dtype), pair_pos.data_ptr(),
+                                  _ptr(pair_w), top, _ptr(shared), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                  T, n, seq_of_token.data_ptr(), _stream()), "moe_combine")
 
 
 _device_flags = {}

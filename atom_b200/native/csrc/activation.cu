@@ -75,6 +75,37 @@ __global__ void tanh_kernel(T* __restrict__ x, int64_t n) {
     x[idx] = from_float<T>(tanhf(to_float(x[idx])));
 }
 
+// relu(x)^2 in place.
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ x, int64_t n) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride) {
+    const float z = fmaxf(to_float(x[idx]), 0.f);
+    x[idx] = from_float<T>(z * z);
+  }
+}
+
+// bfloat16, eight numbers per load and store.
+__global__ void relu2_bf16_vec_kernel(uint4* __restrict__ x, int64_t nvec) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec; idx += stride) {
+    uint4 v = x[idx];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h[i]);
+      f.x = fmaxf(f.x, 0.f);
+      f.y = fmaxf(f.y, 0.f);
+      h[i] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+    }
+    x[idx] = v;
+  }
+}
+
 }  // namespace atom
 
 ATOM_EXPORT int atom_tanh(void* x, int dtype, int64_t n, cudaStream_t stream) {
@@ -127,5 +158,25 @@ ATOM_EXPORT int atom_silu_mul(void* out, const void* gu, int dtype, int T, int I
   } else {
     return ATOM_ERR_ARG;
   }
+  return atom::check_launch();
+}
+
+ATOM_EXPORT int atom_relu2(void* x, int dtype, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return ATOM_OK;
+  const int threads = 256;
+  if (dtype == ATOM_BF16 && n % 8 == 0 && (uintptr_t)x % 16 == 0) {
+    int64_t vb = (n / 8 + threads - 1) / threads;
+    if (vb > 148 * 32) vb = 148 * 32;
+    atom::launch_pdl(atom::relu2_bf16_vec_kernel, dim3((int)vb), dim3(threads), 0, stream, (uint4*)x, n / 8);
+    return atom::check_launch();
+  }
+  int64_t blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::relu2_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (float*)x, n);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::relu2_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)x, n);
+  else
+    return ATOM_ERR_ARG;
   return atom::check_launch();
 }

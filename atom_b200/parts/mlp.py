@@ -3,7 +3,8 @@
 Dense with the xIELU activation:  y = W_down act(W_up x),
    act(z) = softplus(p) z^2 + z/2 for z > 0,  (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 otherwise,
 with the two numbers (p, q) a parameter of the layer.
-GELU-gated:  y = W_down (gelu_tanh(W_gate x) * (W_up x)),  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))."""
+GELU-gated:  y = W_down (gelu_tanh(W_gate x) * (W_up x)),  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+Dense with the square of relu:  y = W_down relu(W_up x)^2."""
 from __future__ import annotations
 
 import math
@@ -92,3 +93,28 @@ class DenseXielu(FeedForward):
         z = linear(x, self.w_up_weight, None, ws.get("ffn.up", (T, self.intermediate_size), dt))
         native.xielu(z, z, self._ap, self._aq)
         return linear(z, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))
+
+
+@register("ffn", "dense_relu2")
+class DenseRelu2(FeedForward):
+    """y = W_down relu(W_up x)^2."""
+    graph_safe = True
+    takes_scaled_rows = True      # x may be ScaledRows: the first product finishes the norm
+    defers_output = True          # forward(..., defer=True) may hand the last product on unrun
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+
+    def params(self) -> Dict[str, ParamSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return {"up.weight": ParamSpec((I, H)), "down.weight": ParamSpec((H, I))}
+
+    def forward(self, x, step, defer=False):
+        T = x.shape[0]
+        ws, dt = self.rt.workspace, self.rt.dtype
+        z = linear(x, self.w_up_weight, None, ws.get("ffn.up", (T, self.intermediate_size), dt))
+        native.relu2_(z)
+        out = ws.get("ffn.out", (T, self.hidden_size), dt)
+        if defer and may_defer(z, self.w_down_weight):
+            return PendingProduct(z, self.w_down_weight, None, out)
+        return linear(z, self.w_down_weight, None, out)

@@ -25,11 +25,17 @@ from .spec import ParamSpec
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, size: int, eps: float):
-        self.size, self.eps = size, eps
+    def __init__(self, size: int, eps: float, weight_offset: float = 0.0):
+        """weight_offset: the stored weight lies around zero and the factor is weight_offset + w (1 + w for a
+        design that stores its norm weights so); the sum is formed once after loading, in 32-bit."""
+        self.size, self.eps, self.weight_offset = size, eps, float(weight_offset)
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), role="vector", init="norm")}
+        return {"weight": ParamSpec((self.size,), role="vector", init="normal" if self.weight_offset else "norm")}
+
+    def after_load(self) -> None:
+        if self.weight_offset:
+            self.w_weight = (self.w_weight.float() + self.weight_offset).contiguous()
 
     fuses_products = True      # add_norm takes a PendingProduct as delta and the keyword scaled_ok
 

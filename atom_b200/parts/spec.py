@@ -118,8 +118,9 @@ class CacheEntry:
 class CacheNeed:
     """What a mixer keeps per request between steps.
 
-    kind "pages": ``entries`` for every position (or for the last ``window`` positions), held in
-                  pages.  Giving ``num_kv_heads`` and ``head_dim`` instead stands for the two
+    kind "pages": ``entries`` for every position (or for the last ``window`` positions, and with
+                  ``keep_first`` also for the request's first positions, which a window never drops),
+                  held in pages.  Giving ``num_kv_heads`` and ``head_dim`` instead stands for the two
                   entries "k" and "v" of that shape each.
     kind "state": one array of fixed shape per request, held in a slot.
     Either kind may also name ``states``: arrays of fixed shape per request (``CacheEntry`` with the
@@ -132,6 +133,7 @@ class CacheNeed:
     num_kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None
+    keep_first: int = 0
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
     entries: Tuple[CacheEntry, ...] = ()
@@ -153,7 +155,7 @@ class CacheNeed:
 
     def group_key(self) -> Tuple:
         if self.kind == "pages":
-            return ("pages", self.entries, self.window)
+            return ("pages", self.entries, self.window) + ((self.keep_first,) if self.window and self.keep_first else ())
         return ("state", self.state_shape, self.state_dtype)
 
     @property
@@ -178,7 +180,7 @@ class CacheNeed:
             states += [CacheEntry(f"{n}.{e.name}", e.shape, e.dtype) for e in c.states]
         if pages:
             c = pages[0][1]
-            return CacheNeed("pages", window=c.window, entries=c.entries, states=tuple(states))
+            return CacheNeed("pages", window=c.window, keep_first=c.keep_first, entries=c.entries, states=tuple(states))
         if states:
             return CacheNeed("state", states=tuple(states))
         return None
