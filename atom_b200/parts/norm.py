@@ -34,6 +34,7 @@ class RMSNorm(Norm):
         return {"weight": ParamSpec((self.size,), role="vector", init="normal" if self.weight_offset else "norm")}
 
     def after_load(self) -> None:
+        super().after_load()
         if self.weight_offset:
             self.w_weight = (self.w_weight.float() + self.weight_offset).contiguous()
 
