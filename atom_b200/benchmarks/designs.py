@@ -1,7 +1,7 @@
-"""Prefill and decode throughput of the Nurinex and Mugulorn designs beside Qwen3 dense at equal sizes.
+"""Prefill and decode throughput of the Nurinex, Mugulorn and Simivik designs beside Qwen3 dense at equal sizes.
 
     python -m atom_b200.benchmarks.designs [--sizes 1024x8,2048x16] [--layers 4] [--prefill 2048]
-                                           [--batch 8] [--context 2048] [--kernels] [--only qwen3,mugulorn]
+                                           [--batch 8] [--context 2048] [--kernels] [--only qwen3,simivik]
 
 For each size (width x attention heads; head size 128, four query heads to a kv head, feed-forward three
 times the width, vocabulary 32768) two engines are built with random bfloat16 weights and the same number
@@ -9,7 +9,11 @@ of layers: Qwen3 dense, and Nurinex whose attention has the same heads and whose
 heads of 64 channels; and Mugulorn, whose layers alternate attention through a latent (the same heads,
 128 + 64 numbers per head, values of 128, a latent of width / 4, queries through width / 2, a window of 1024;
 every second attention layer reads the cache of the one before) with a gated linear recurrence of the width's
-channels in as many blocks as heads behind a convolution of 4 taps.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
+channels in as many blocks as heads behind a convolution of 4 taps; and Simivik, whose layers are attention behind
+a convolution of 4 taps (the same heads, all 128 numbers rotated, scores capped at 50, a window of 1024 that keeps the
+first 64 tokens) with a dense relu-squared feed-forward, lightning attention (the same heads, 128 numbers per key and
+value) with 16 experts of the width's size of which 2 are used beside a shared one (three times the width per token,
+as the dense ones), attention with the dense feed-forward, attention with the experts, and so on.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
 one step, and decode steps of ``--batch`` requests whose caches hold ``--context`` tokens (captured graphs,
 as the engine runs them).  With ``--kernels`` the kernels of one prefill step and of one decode step are
 listed with their summed device time (the engine's profiler hook), which is what the per-kernel rooflines
@@ -69,6 +73,17 @@ def mugulorn_config(width: int, heads: int, layers: int) -> dict:
             owner = None
     return {"architecture": "Mugulorn", "vocab": VOCAB, "width": width, "residual_mult": 0.5, "embedding": {"scale": 1.0},
             "norm": {"eps": 1e-5}, "layers": out}
+
+
+def simivik_config(width: int, heads: int, layers: int) -> dict:
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+           "conv": 4, "rot": {"base": 1000000.0, "dims": 128}, "mask": {"size": 1024, "keep_first": 64}}
+    lin = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 7 * h / max(1, heads - 1)) for h in range(heads)]}
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": width}, "shared": {"ff": width}}
+    kinds = [("attention", att, dense), ("lightning", lin, moe), ("attention", att, dense), ("attention", att, moe)]
+    return {"architecture": "Simivik", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds[i % 4] for i in range(layers))]}
 
 
 def _runner(cfg: dict, pages: int, max_len: int, batch: int):
@@ -171,9 +186,9 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--kernels", action="store_true", help="list the kernels of one prefill and one decode step")
-    ap.add_argument("--only", default="qwen3,nurinex,mugulorn", help="the designs to measure, comma-separated")
+    ap.add_argument("--only", default="qwen3,nurinex,mugulorn,simivik", help="the designs to measure, comma-separated")
     args = ap.parse_args(argv)
-    configs = {"qwen3": qwen3_config, "nurinex": nurinex_config, "mugulorn": mugulorn_config}
+    configs = {"qwen3": qwen3_config, "nurinex": nurinex_config, "mugulorn": mugulorn_config, "simivik": simivik_config}
     chosen = [d for d in args.only.split(",") if d]
     if any(d not in configs for d in chosen):
         ap.error(f"--only takes {sorted(configs)}")
