@@ -834,6 +834,69 @@ def window_attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, 
         "window_attention")
 
 
+# ---- the same attention on the tensor cores (csrc/window_attention_tc.cu), compiled per (key size, value size) on
+# first use
+_watc_libs = {}
+_WATC_SIG = [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp, _vp]
+WINDOW_TC = True     # False: the plain kernel also where the tensor-core kernel takes the sizes (measurements, tests)
+WINDOW_TC_ROWS = 64  # query rows of a tile
+
+
+def window_attention_tc_supports(dk: int, dv: int, dtype: torch.dtype) -> bool:
+    """bfloat16; key and value sizes in steps of 16, keys up to 256 and values up to 128 numbers (a warp keeps its
+    16 x value size output in registers)."""
+    return dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and 16 <= dk <= 256 and 16 <= dv <= 128
+
+
+def watc_lib(dk: int, dv: int):
+    key = (dk, dv)
+    l = _watc_libs.get(key)
+    if l is None:
+        with _lock:
+            l = _watc_libs.get(key)
+            if l is None:
+                path = build_variant("window_attention_tc.cu", {"ATOM_WA_DK": dk, "ATOM_WA_DV": dv})
+                l = ctypes.CDLL(path)
+                l.atom_window_attention_tc.argtypes = _WATC_SIG
+                l.atom_window_attention_tc.restype = ctypes.c_int
+                got = [ctypes.c_int() for _ in range(2)]
+                l.atom_watc_sizes(*[ctypes.byref(g) for g in got])
+                if tuple(g.value for g in got) != key:
+                    raise NativeBuildError(f"{path} was built for other sizes")
+                _watc_libs[key] = l
+    return l
+
+
+def window_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                        block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                        cu_q: torch.Tensor, num_seqs: int, nh: int, nkv: int, dk: int, dv: int, scale: float,
+                        softcap: float = 0.0, window: int = 0, keep_first: int = 0, nsplit: int = 1,
+                        scratch: Optional[torch.Tensor] = None) -> None:
+    """``window_attention`` on the tensor cores: tiles of 64 consecutive tokens of a request and one head (cu_q:
+    [num_seqs + 1] first token row of every request); with nsplit > 1 a tile's keys are shared out among nsplit
+    CTAs and put together by the merge kernel of ``attention_mixed``.  Sizes as ``window_attention_tc_supports``."""
+    _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token, cu_q, scratch)
+    T = q.shape[0]
+    page_size = k_pages.shape[2]
+    assert q.stride(1) == 1 and q.shape[1] == nh * dk and out.is_contiguous() and out.shape == (T, nh * dv)
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, dk) and tuple(v_pages.shape[1:]) == (nkv, page_size, dv)
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and cu_q.numel() >= num_seqs + 1
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert nsplit == 1 or (scratch is not None and scratch.dtype == torch.float32
+                           and scratch.numel() >= attention_mixed_scratch_elems(T, nh, dv, nsplit))
+    units = -(-T // WINDOW_TC_ROWS) + num_seqs
+    _check(watc_lib(dk, dv).atom_window_attention_tc(
+        out.data_ptr(), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+        block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(), cu_q.data_ptr(), num_seqs, units,
+        nh, nkv, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first),
+        int(nsplit), _ptr(scratch) if nsplit > 1 else None, _stream()), "window_attention_tc")
+    if nsplit > 1:
+        _check(lib().atom_attention_mixed_merge(out.data_ptr(), dtype_code(out.dtype), scratch.data_ptr(),
+                                                seq_of_token.data_ptr(), T, nh, dv, nsplit, _stream()),
+               "attention_mixed_merge")
+
+
 def lightning_supports(dk: int, dv: int) -> bool:
     return bool(lib().atom_lightning_supports(dk, dv))
 

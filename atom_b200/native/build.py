@@ -77,7 +77,7 @@ def build_dir() -> str:
 
 # Sources that are compiled per variant (one library per value of their -D parameters), on
 # first use by a model that needs that variant; everything else goes into the core library.
-VARIANT_SOURCES = {"attention_flash.cu", "attention_mixed_tc.cu"}
+VARIANT_SOURCES = {"attention_flash.cu", "attention_mixed_tc.cu", "window_attention_tc.cu"}
 
 
 def sources() -> List[str]:
@@ -228,6 +228,8 @@ PREBUILT_MIXED_HEADS = (
     {"ATOM_MH_NH": 16, "ATOM_MH_NKV": 4, "ATOM_MH_DK": 128, "ATOM_MH_DV": 128},
     {"ATOM_MH_NH": 4, "ATOM_MH_NKV": 2, "ATOM_MH_DK": 16, "ATOM_MH_DV": 32},
 )
+# Sizes of the windowed attention on the tensor cores that the build check compiles ahead of use.
+PREBUILT_WINDOW_HEADS = ({"ATOM_WA_DK": 128, "ATOM_WA_DV": 128}, {"ATOM_WA_DK": 64, "ATOM_WA_DV": 64})
 
 
 def build_all(verbose: bool = True) -> str:
@@ -236,6 +238,7 @@ def build_all(verbose: bool = True) -> str:
     with concurrent.futures.ThreadPoolExecutor(max(1, min(len(PREBUILT_HEAD_DIMS), os.cpu_count() or 1))) as ex:
         list(ex.map(lambda hd: build_variant("attention_flash.cu", {"ATOM_HD": hd}, verbose), PREBUILT_HEAD_DIMS))
         list(ex.map(lambda d: build_variant("attention_mixed_tc.cu", d, verbose), PREBUILT_MIXED_HEADS))
+        list(ex.map(lambda d: build_variant("window_attention_tc.cu", d, verbose), PREBUILT_WINDOW_HEADS))
     return core
 
 

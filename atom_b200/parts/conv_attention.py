@@ -69,6 +69,23 @@ class ConvWindowAttention(Mixer):
                          entries=(CacheEntry("k", (self.nkv, self.dk)), CacheEntry("v", (self.nkv, self.dv))),
                          states=states)
 
+    def launch_plan(self, step):
+        """Into how many shares the tensor-core kernel cuts the key tiles of every (tile of 64 tokens, head), or 0 for
+        the plain kernel.  Where the tiles do not fill the device (decoding, short portions) their keys are shared
+        out, in shares of at least 128."""
+        key = ("conv_window_attention", self.nh, self.dk, self.dv, self.window or 0, self.keep_first)
+        plan = step.plans.get(key)
+        if plan is None:
+            if native.WINDOW_TC and native.window_attention_tc_supports(self.dk, self.dv, self.rt.dtype):
+                longest = min(step.max_ctx_len, self.window + self.keep_first) if self.window else step.max_ctx_len
+                tiles = step.num_tokens if step.max_q_len <= 1 else \
+                    -(-step.num_tokens // native.WINDOW_TC_ROWS) + step.num_seqs - 1
+                plan = native.attention_mixed_splits(tiles * self.nh, longest, per_sm=2, min_share=128)
+            else:
+                plan = 0
+            step.plans[key] = plan
+        return plan
+
     def forward(self, x, step, cache, writes_cache, defer=False):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
@@ -87,8 +104,17 @@ class ConvWindowAttention(Mixer):
         if conv_state is not None and writes_cache:
             native.conv_state_update(conv_state, qkv, step.cu_q, step.state_slots, step.num_seqs)
         o = ws.get("cwa.o", (T, nh * dv), dt)
-        native.window_attention(o, q, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token, nh, nkv,
-                                dk, dv, self.scale, self.softcap, self.window or 0, self.keep_first)
+        nsplit = self.launch_plan(step)
+        if nsplit:
+            scratch = None
+            if nsplit > 1:
+                scratch = ws.get("cwa.splits", (native.attention_mixed_scratch_elems(T, nh, dv, nsplit),), torch.float32)
+            native.window_attention_tc(o, q, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token,
+                                       step.cu_q, step.num_seqs, nh, nkv, dk, dv, self.scale, self.softcap,
+                                       self.window or 0, self.keep_first, nsplit, scratch)
+        else:
+            native.window_attention(o, q, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token, nh, nkv,
+                                    dk, dv, self.scale, self.softcap, self.window or 0, self.keep_first)
         out = ws.get("cwa.out", (T, self.hidden_size), dt)
         if defer and may_defer(o, self.w_o_weight):
             return PendingProduct(o, self.w_o_weight, None, out)

@@ -189,9 +189,16 @@ def _attention_part(case, dtype, width=72, seed=0):
     return part, m, P, width
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain"])
 @pytest.mark.parametrize("case", ATT_CASES)
-def test_attention_part_under_every_cut(case, dtype):
+def test_attention_part_under_every_cut(case, dtype, monkeypatch):
+    """(bfloat16 runs the tensor-core kernel where it takes the sizes; "bfloat16-plain" the plain kernel there too.)"""
+    from atom_b200 import native
+    if dtype.endswith("-plain"):
+        if not native.window_attention_tc_supports(case[2], case[3], torch.bfloat16):
+            pytest.skip("these sizes run the plain kernel anyway")
+        monkeypatch.setattr(native, "WINDOW_TC", False)
+        dtype = "bfloat16"
     part, m, P, W = _attention_part(case, dtype)
     page, lens = case[8], dict(zip("abc", case[9]))
     g = torch.Generator().manual_seed(sum(case[9]))
@@ -216,7 +223,14 @@ def _win_pages(T, G, page, dk, dv, dtype, seed=0, extra=5):
     return table, kp, vp
 
 
-def _run_window_attention(q, k, v, scale, cap, window, keep, dtype, page, cuts):
+def _kernels(dk, dv, dtype):
+    """The kernels that take these sizes: the plain one always; the tensor-core one where it does, alone on a tile's
+    keys and with the keys shared out among three and among seven CTAs."""
+    from atom_b200 import native
+    return ["plain", "tc1", "tc3", "tc7"] if native.window_attention_tc_supports(dk, dv, _dt(dtype)) else ["plain"]
+
+
+def _run_window_attention(q, k, v, scale, cap, window, keep, dtype, page, cuts, kernel="plain"):
     """q [T, H, dk], k [T, G, dk], v [T, G, dv] of ONE request, keys and values laid into scrambled pages; the queries
     are run in portions ``cuts`` (the keys of later portions are not in the pages yet)."""
     from atom_b200 import native
@@ -236,8 +250,16 @@ def _run_window_attention(q, k, v, scale, cap, window, keep, dtype, page, cuts):
         kp[pg, :, j % page] = k[at:at + n].to(dt).to(DEV)
         vp[pg, :, j % page] = v[at:at + n].to(dt).to(DEV)
         o = torch.zeros(n, H * dv, dtype=dt, device=DEV)
-        native.window_attention(o, q[at:at + n].reshape(n, H * dk).to(dt).to(DEV).contiguous(), kp, vp, table,
-                                _i32(range(at, at + n)), _i32([0] * n), H, G, dk, dv, scale, cap, window, keep)
+        qd = q[at:at + n].reshape(n, H * dk).to(dt).to(DEV).contiguous()
+        if kernel.startswith("tc"):
+            ns = int(kernel[2:])
+            scratch = torch.full((native.attention_mixed_scratch_elems(n, H, dv, ns),), float("nan"), dtype=torch.float32,
+                                 device=DEV) if ns > 1 else None
+            native.window_attention_tc(o, qd, kp, vp, table, _i32(range(at, at + n)), _i32([0] * n), _i32([0, n]), 1, H, G,
+                                       dk, dv, scale, cap, window, keep, ns, scratch)
+        else:
+            native.window_attention(o, qd, kp, vp, table, _i32(range(at, at + n)), _i32([0] * n), H, G, dk, dv, scale,
+                                    cap, window, keep)
         out[at:at + n] = o
         at += n
     assert at == T
@@ -290,15 +312,18 @@ def test_single_keys_at_the_windows_edge_and_among_the_kept_tokens(window, keep,
         cut_sets.append([needle + 1] + [1] * (T - needle - 1))
         cut_sets.append([1] * (keep + window + 3) + [T])
     for cuts in cut_sets:
-        got = _run_window_attention(q, k, v, 1.0, 0.0, window, keep, dtype, page, cuts)
-        what = f"window {window}, kept {keep}, cuts {cuts[:4]}"
-        for col, pos in marks.items():
-            for i in range(T):
-                if sees(i, pos):
-                    assert float(got[i, :, col].min()) > 0.25, f"{what}: key {pos} is lost at {i}"
-                else:
-                    assert float(got[i, :, col].abs().max()) == 0, f"{what}: key {pos} is seen from {i}"
-        _close(got, want, dtype, what, f32=2e-5, bf16=1e-2)
+        for kernel in _kernels(dk, dv, dtype):
+            if kernel in ("tc3", "tc7") and len(cuts) > 20:
+                continue
+            got = _run_window_attention(q, k, v, 1.0, 0.0, window, keep, dtype, page, cuts, kernel)
+            what = f"{kernel}, window {window}, kept {keep}, cuts {cuts[:4]}"
+            for col, pos in marks.items():
+                for i in range(T):
+                    if sees(i, pos):
+                        assert float(got[i, :, col].min()) > 0.25, f"{what}: key {pos} is lost at {i}"
+                    else:
+                        assert float(got[i, :, col].abs().max()) == 0, f"{what}: key {pos} is seen from {i}"
+            _close(got, want, dtype, what, f32=2e-5, bf16=1e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -315,9 +340,36 @@ def test_scores_are_capped_before_the_softmax(dtype):
     for cap, scale in ((2.0, 1.0), (0.0, 0.25), (7.5, 0.5)):
         s = q[1, :, 0] * scale
         want = torch.sigmoid(cap * torch.tanh(s / cap) if cap else s)
-        got = _run_window_attention(q, k, v, scale, cap, 0, 0, dtype, 8, [2])
-        _close(got[1, :, 0], want, dtype, f"cap {cap}", scale=1.0, f32=1e-6, bf16=4e-3)
-        assert cap == 0 or float(got[1, 2, 0]) < 1 / (1 + math.exp(-cap)) + 1e-3
+        for kernel in _kernels(dk, dv, dtype):
+            got = _run_window_attention(q, k, v, scale, cap, 0, 0, dtype, 8, [2], kernel)
+            _close(got[1, :, 0], want, dtype, f"{kernel}, cap {cap}", scale=1.0, f32=1e-6, bf16=4e-3)
+            assert cap == 0 or float(got[1, 2, 0]) < 1 / (1 + math.exp(-cap)) + 1e-3
+
+
+TC_CASES = [  # H, G, dk, dv, window, keep, cap, page, T
+    (4, 2, 16, 32, 24, 5, 5.0, 16, 200), (8, 2, 64, 64, 128, 16, 30.0, 32, 333), (6, 3, 96, 64, 72, 70, 50.0, 16, 300),
+    (4, 1, 128, 128, 0, 0, 0.0, 16, 270), (2, 2, 256, 16, 65, 64, 3.0, 8, 200), (3, 1, 48, 112, 1, 1, 0.0, 16, 150),
+    (5, 5, 32, 80, 200, 130, 10.0, 64, 520), (16, 4, 128, 128, 100, 3, 20.0, 16, 600),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tensor_core_attention_against_plain_scores(case):
+    """The tensor-core kernel on sharp random scores: prompts of several tiles, portions that start in the middle of a
+    tile of keys, single tokens, and the keys shared out among CTAs (also more CTAs than there are key tiles)."""
+    H, G, dk, dv, window, keep, cap, page, T = case
+    g = torch.Generator().manual_seed(T + dk)
+    q = _rounded(torch.randn(T, H, dk, generator=g), "bfloat16")
+    k = _rounded(torch.randn(T, G, dk, generator=g), "bfloat16")
+    v = _rounded(torch.randn(T, G, dv, generator=g), "bfloat16")
+    scale = 3.0 / dk ** 0.5
+    want = _plain_scores(q, k, v, scale, cap, window, keep)
+    kernels = _kernels(dk, dv, "bfloat16")
+    assert "tc1" in kernels
+    for kernel in kernels:
+        for cuts in ([T], [T - 9] + [1] * 9, [13, 64, 5, 2, 129, 2, 70, 3, 17] * 8):
+            got = _run_window_attention(q, k, v, scale, cap, window, keep, "bfloat16", page, cuts, kernel)
+            _close(got, want, "bfloat16", f"{kernel}, cuts {cuts[:3]}", bf16=1e-2)
 
 
 # ============================================================================= lightning attention
