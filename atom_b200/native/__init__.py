@@ -94,7 +94,7 @@ _SIGNATURES = {
     "atom_lightning_gate_norm": [_vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _f, _vp, _vp],
     "atom_moe_route": [_vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "atom_moe_place": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
-    "atom_moe_gemm": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "atom_moe_gemm": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "atom_moe_combine": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i64, _i, _i, _vp, _vp],
     "atom_rmsnorm": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
@@ -975,11 +975,15 @@ def moe_place(ids: torch.Tensor, wts: torch.Tensor, E: int, counts: torch.Tensor
                                 row_token.data_ptr(), row_w.data_ptr(), pair_pos.data_ptr(), _stream()), "moe_place")
 
 
+MOE_TC = True        # False: the plain product also in bfloat16 (measurements, tests)
+
+
 def moe_gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, gated: bool = False,
              row_token: Optional[torch.Tensor] = None, row_w: Optional[torch.Tensor] = None) -> None:
     """out[r] = A[r] w[e]^T for the places r of every expert e (offsets [E + 1]); w [E, N or 2 N, K].  With row_token
     and row_w, A[r] = row_w[r] * a[row_token[r]] (rows picked from the step's rows, weighted on the way in); else
-    A = a by place.  gated: w[e] = [gate ; up], out = silu(gate) * up."""
+    A = a by place.  gated: w[e] = [gate ; up], out = silu(gate) * up.  bfloat16 with K and the row stride in steps
+    of 8 runs on the tensor cores, everything else on plain FMAs."""
     _cuda(out, a, w, offsets, row_token, row_w)
     R, N = out.shape
     E, K = w.shape[0], w.shape[2]
@@ -987,7 +991,7 @@ def moe_gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, offsets: torch
     assert a.shape[1] == K and out.dtype == a.dtype == w.dtype and (row_token is not None or a.shape[0] >= R)
     _check(lib().atom_moe_gemm(out.data_ptr(), a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(),
                                offsets.data_ptr(), _ptr(row_token), _ptr(row_w), R, E, N, K, int(gated),
-                               int(row_token is not None), _stream()), "moe_gemm")
+                               int(row_token is not None), int(MOE_TC), _stream()), "moe_gemm")
 
 
 def moe_combine(out: torch.Tensor, y: torch.Tensor, pair_pos: torch.Tensor, top: int,

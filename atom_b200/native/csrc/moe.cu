@@ -8,7 +8,8 @@
 //   moe_gemm_kernel     out[r] = A[r] W_e^T for the rows r of every expert e, tile by tile.  A[r] is either a dense
 //                       row or weight_r * x[token_r] (the weight on the expert's INPUT); with GATED, W_e is
 //                       [gate ; up] and the output is silu(gate) * up.  32-bit sums, each output summed over k in
-//                       order, so a row's result does not depend on the rows beside it
+//                       order, so a row's result does not depend on the rows beside it; in bfloat16 on the tensor
+//                       cores (moe_gemm_tc_kernel), in 32-bit and for odd sizes with plain FMAs
 //   moe_combine_kernel  out[t] = sum over t's choices of (weight *) y[place] (+ sigmoid(gate logit_t) * shared[t])
 #include "common.cuh"
 
@@ -233,6 +234,190 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
   }
 }
 
+// ---- the same product in bfloat16 on the tensor cores -----------------------------------------------------------
+// A CTA of 4 warps takes BM rows of one expert (64, or 16 in steps of few rows, where the warps share out the
+// columns instead of the rows) and 64 output columns (with GATED the 64 gate rows and the 64 up rows of W_e), and
+// walks K in steps of 32: tiles of A and W_e come into shared memory with cp.async, three steps deep (gathered rows
+// pass through registers, where they are weighted and rounded); mma.sync m16n8k16 with 32-bit sums.  Every output is
+// summed over k in the same order whatever the tile, so a row's result does not depend on the rows beside it.
+constexpr int kTcBN = 64, kTcBK = 32, kTcLD = kTcBK + 8, kTcStages = 3, kTcThreads = 128;
+
+__device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void moe_mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void moe_cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+
+constexpr size_t moe_tc_smem(int bm, bool gated) {
+  return sizeof(__nv_bfloat16) * kTcStages * ((size_t)bm + (gated ? 2 : 1) * kTcBN) * kTcLD;
+}
+
+template <bool GATED, bool GATHER, int BM>
+__global__ void __launch_bounds__(kTcThreads)
+moe_gemm_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ A, int64_t lda,
+                   const __nv_bfloat16* __restrict__ W, const int* __restrict__ offsets,
+                   const int* __restrict__ row_token, const float* __restrict__ row_w, int E, int N, int K) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  constexpr int WM = BM / 16, WN = 4 / WM;                 // warps along the rows and along the columns
+  constexpr int NT = kTcBN / WN / 8;                        // 8-column tiles of a warp
+  constexpr int BROWS = (GATED ? 2 : 1) * kTcBN;
+  constexpr int STAGE = (BM + BROWS) * kTcLD;
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  __nv_bfloat16* sm = reinterpret_cast<__nv_bfloat16*>(moe_smem);
+  __shared__ int64_t a_row[BM];
+  __shared__ float a_mul[BM];
+  int e, row0, rows;
+  if (!moe_find_tile(blockIdx.x, offsets, E, BM, e, row0, rows)) return;
+  const int n0 = blockIdx.y * kTcBN;
+  const __nv_bfloat16* We = W + (int64_t)e * (GATED ? 2 : 1) * N * K;
+  if (threadIdx.x < BM) {
+    const int r = threadIdx.x;
+    if (r < rows) {
+      a_row[r] = (GATHER ? (int64_t)row_token[row0 + r] : (int64_t)(row0 + r)) * lda;
+      a_mul[r] = GATHER ? row_w[row0 + r] : 1.f;
+    } else {
+      a_row[r] = -1;
+      a_mul[r] = 0.f;
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = warp % WM, wn = warp / WM;
+
+  auto load = [&](int stage, int k0) {
+    __nv_bfloat16* As = sm + stage * STAGE;
+    __nv_bfloat16* Bs = As + BM * kTcLD;
+    constexpr int KC = kTcBK / 8;
+    for (int idx = threadIdx.x; idx < BM * KC; idx += kTcThreads) {
+      const int r = idx / KC, c = idx - r * KC;
+      const bool valid = a_row[r] >= 0 && k0 + c * 8 < K;
+      __nv_bfloat16* dst = As + r * kTcLD + c * 8;
+      if (GATHER) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) {
+          raw = *reinterpret_cast<const uint4*>(A + a_row[r] + k0 + c * 8);
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+          const float m = a_mul[r];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            // the weighted row is rounded to the activation type, as a row that a kernel of its own had written
+            const float2 f = __bfloat1622float2(h2[i]);
+            h2[i] = __floats2bfloat162_rn(f.x * m, f.y * m);
+          }
+        }
+        *reinterpret_cast<uint4*>(dst) = raw;
+      } else {
+        moe_cp_async16(dst, A + (valid ? a_row[r] + k0 + c * 8 : 0), valid);
+      }
+    }
+    for (int idx = threadIdx.x; idx < BROWS * KC; idx += kTcThreads) {
+      const int r = idx / KC, c = idx - r * KC;
+      const int n = n0 + (r % kTcBN);
+      const bool valid = n < N && k0 + c * 8 < K;
+      const int64_t wrow = (GATED && r >= kTcBN) ? (int64_t)N + n : (int64_t)n;
+      moe_cp_async16(Bs + r * kTcLD + c * 8, We + (valid ? wrow * K + k0 + c * 8 : 0), valid);
+    }
+  };
+
+  float g[NT][4], u[GATED ? NT : 1][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) g[i][0] = g[i][1] = g[i][2] = g[i][3] = 0.f;
+#pragma unroll
+  for (int i = 0; i < (GATED ? NT : 1); ++i) u[i][0] = u[i][1] = u[i][2] = u[i][3] = 0.f;
+
+  const int steps = (K + kTcBK - 1) / kTcBK;
+#pragma unroll
+  for (int s = 0; s < kTcStages - 1; ++s) {
+    if (s < steps) load(s, s * kTcBK);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  for (int it = 0; it < steps; ++it) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(kTcStages - 2));
+    __syncthreads();                                  // step `it` has landed, and the stage loaded below is free
+    if (it + kTcStages - 1 < steps) load((it + kTcStages - 1) % kTcStages, (it + kTcStages - 1) * kTcBK);
+    asm volatile("cp.async.commit_group;\n" ::);
+    const __nv_bfloat16* As = sm + (it % kTcStages) * STAGE;
+    const __nv_bfloat16* Bs = As + BM * kTcLD;
+#pragma unroll
+    for (int kk = 0; kk < kTcBK / 16; ++kk) {
+      uint32_t a[4];
+      moe_ldmatrix_x4(a, As + (wm * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kTcLD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        const int brow = wn * (kTcBN / WN) + np * 16 + (lane >> 4) * 8 + (lane & 7);
+        uint32_t b[4];
+        moe_ldmatrix_x4(b, Bs + brow * kTcLD + kk * 16 + ((lane >> 3) & 1) * 8);
+        moe_mma_bf16(g[2 * np], a, b[0], b[1]);
+        moe_mma_bf16(g[2 * np + 1], a, b[2], b[3]);
+        if (GATED) {
+          moe_ldmatrix_x4(b, Bs + (kTcBN + brow) * kTcLD + kk * 16 + ((lane >> 3) & 1) * 8);
+          moe_mma_bf16(u[2 * np], a, b[0], b[1]);
+          moe_mma_bf16(u[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = wm * 16 + (lane >> 2) + (i >> 1) * 8;
+      const int n = n0 + wn * (kTcBN / WN) + nt * 8 + (lane & 3) * 2 + (i & 1);
+      if (r < rows && n < N) {
+        float v = g[nt][i];
+        if (GATED) {
+          // gate and up are rounded to the activation type first, as the unfused product hands them on
+          const float gr = __bfloat162float(__float2bfloat16_rn(v));
+          const float ur = __bfloat162float(__float2bfloat16_rn(u[GATED ? nt : 0][i]));
+          v = gr / (1.f + expf(-gr)) * ur;
+        }
+        out[(int64_t)(row0 + r) * N + n] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+template <bool GATED, bool GATHER, int BM>
+static void moe_gemm_tc_launch_one(__nv_bfloat16* out, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
+                                   const int* offsets, const int* row_token, const float* row_w, int R, int E, int N,
+                                   int K, cudaStream_t stream) {
+  dim3 grid((R + BM - 1) / BM + E, (N + kTcBN - 1) / kTcBN);
+  launch_pdl(moe_gemm_tc_kernel<GATED, GATHER, BM>, grid, dim3(kTcThreads), moe_tc_smem(BM, GATED), stream, out, A, lda,
+             W, offsets, row_token, row_w, E, N, K);
+}
+
+// Rows per tile: 16 while the step's rows are few (decoding: an expert gets a handful), else 64.
+static int moe_gemm_tc_launch(__nv_bfloat16* out, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
+                              const int* offsets, const int* row_token, const float* row_w, int R, int E, int N, int K,
+                              int gated, int gather, cudaStream_t stream) {
+  const bool small = R <= 16 * E;
+#define ATOM_MOE_TC(G, H)                                                                                       \
+  do {                                                                                                          \
+    if (small) moe_gemm_tc_launch_one<G, H, 16>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream); \
+    else moe_gemm_tc_launch_one<G, H, 64>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);       \
+  } while (0)
+  if (gated && gather) ATOM_MOE_TC(true, true);
+  else if (gated) ATOM_MOE_TC(true, false);
+  else if (gather) ATOM_MOE_TC(false, true);
+  else ATOM_MOE_TC(false, false);
+#undef ATOM_MOE_TC
+  return check_launch();
+}
+
 template <typename T>
 static int moe_gemm_launch(T* out, const T* A, int64_t lda, const T* W, const int* offsets, const int* row_token,
                            const float* row_w, int R, int E, int N, int K, int gated, int gather, cudaStream_t stream) {
@@ -271,12 +456,15 @@ ATOM_EXPORT int atom_moe_place(const int* ids, const float* wts, int pairs, int 
 // R: the most rows there can be (rows of the step x top); the kernel finds the real ones from `offsets`.
 ATOM_EXPORT int atom_moe_gemm(void* out, const void* A, int dtype, int64_t lda, const void* W, const int* offsets,
                               const int* row_token, const float* row_w, int R, int E, int N, int K, int gated,
-                              int gather, cudaStream_t stream) {
+                              int gather, int tc, cudaStream_t stream) {
   if (R <= 0) return ATOM_OK;
   if (E <= 0 || N <= 0 || K <= 0 || (gather && (!row_token || !row_w))) return ATOM_ERR_ARG;
   if (dtype == ATOM_F32)
     return atom::moe_gemm_launch<float>((float*)out, (const float*)A, lda, (const float*)W, offsets, row_token, row_w,
                                         R, E, N, K, gated, gather, stream);
+  if (dtype == ATOM_BF16 && tc && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0)
+    return atom::moe_gemm_tc_launch((__nv_bfloat16*)out, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, offsets,
+                                    row_token, row_w, R, E, N, K, gated, gather, stream);
   if (dtype == ATOM_BF16)
     return atom::moe_gemm_launch<__nv_bfloat16>((__nv_bfloat16*)out, (const __nv_bfloat16*)A, lda,
                                                 (const __nv_bfloat16*)W, offsets, row_token, row_w, R, E, N, K, gated,

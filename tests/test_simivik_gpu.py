@@ -487,18 +487,25 @@ EXPERT_CASES = [  # width, E, top, ff, shared, score, renormalize, weight_on, sh
     (72, 40, 4, 24, None, "softmax", True, "output", False, 130),
     (80, 7, 2, 52, 16, "softmax", False, "output", False, 50),
     (128, 16, 5, 64, None, "sigmoid", True, "input", False, 2),
+    (192, 4, 2, 200, 72, "sigmoid", False, "input", True, 700),
+    (136, 3, 1, 48, None, "sigmoid", False, "input", False, 260),
 ]
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain"])
 @pytest.mark.parametrize("case", EXPERT_CASES)
-def test_routed_experts_part(case, dtype):
+def test_routed_experts_part(case, dtype, monkeypatch):
     """Scores, choice, weights on the way in (or out), the shared expert and its gate; rows of one step go to experts
-    in any numbers, some experts get none."""
+    in any numbers, some experts get none.  (bfloat16 runs the experts' products on the tensor cores where the sizes
+    are multiples of 8, "bfloat16-plain" on plain FMAs there too.)"""
+    from atom_b200 import native
     from atom_b200.parts import registry
     from atom_b200.parts.spec import PartSpec
 
     W, E, top, ff, shared, score, renorm, weight_on, sgate, T = case
+    if dtype.endswith("-plain"):
+        monkeypatch.setattr(native, "MOE_TC", False)
+        dtype = "bfloat16"
     part = registry.build("ffn", PartSpec("routed_experts", dict(
         hidden_size=W, num_experts=E, top=top, intermediate_size=ff, shared_size=shared, score=score, renormalize=renorm,
         weight_on=weight_on, shared_gate=sgate)))
