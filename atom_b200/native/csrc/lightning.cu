@@ -40,6 +40,13 @@ __device__ __forceinline__ bool find_run(int x, const int* __restrict__ cu_q, in
   return false;
 }
 
+// Key channel of register m of a thread of slice 0..3: with KPT a multiple of 4 a thread holds runs of four channels
+// in a row (one 16-byte load of shared memory a run), else every fourth channel.
+template <int KPT>
+__device__ __forceinline__ int lt_channel(int slice, int m) {
+  return KPT % 4 == 0 ? (slice + 4 * (m / 4)) * 4 + (m % 4) : slice + 4 * m;
+}
+
 // proj rows: [q (H dk) | k (H dk) | v (H dv) | ...], row stride ld.  out [T, H dv] float32.  state [slots, H, dk, dv].
 // scratch [run slots, H, dk, dv].
 template <typename T, int KPT, int MODE>
@@ -51,9 +58,10 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
   atom::pdl_trigger();
   atom::pdl_wait();
   extern __shared__ __align__(16) float lt_smem[];
-  float* ks = lt_smem;                          // [kLtStage][dk]
-  float* qs = ks + kLtStage * dk;               // [kLtStage][dk]
-  float* vs = qs + kLtStage * dk;               // [kLtStage][kLtCols]
+  const int dkp = (dk + 3) & ~3;                // rows of k and q are padded with zeros to whole 16-byte loads
+  float* ks = lt_smem;                          // [kLtStage][dkp]
+  float* qs = ks + kLtStage * dkp;              // [kLtStage][dkp]
+  float* vs = qs + kLtStage * dkp;              // [kLtStage][kLtCols]
   int s, r, n_runs;
   if (MODE == 0) {
     s = blockIdx.x;
@@ -82,7 +90,7 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
                                    : scratch + ((int64_t)blockIdx.x * H + h) * mat;
 #pragma unroll
     for (int m = 0; m < KPT; ++m) {
-      const int i = slice + 4 * m;
+      const int i = lt_channel<KPT>(slice, m);
       S[m] = (live && i < dk) ? src[(int64_t)i * dv + c] : 0.f;
     }
   }
@@ -90,11 +98,11 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
   for (int t0 = 0; t0 < len; t0 += kLtStage) {
     const int n = min(kLtStage, len - t0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * dk; idx += kLtThreads) {
-      const int tt = idx / dk, i = idx - tt * dk;
+    for (int idx = threadIdx.x; idx < n * dkp; idx += kLtThreads) {
+      const int tt = idx / dkp, i = idx - tt * dkp;
       const T* row = proj + (int64_t)(first + t0 + tt) * ld;
-      ks[idx] = silu_f(to_float(row[k_off + i]));
-      if (MODE != 1) qs[idx] = silu_f(to_float(row[q_off + i]));
+      ks[idx] = i < dk ? silu_f(to_float(row[k_off + i])) : 0.f;
+      if (MODE != 1) qs[idx] = i < dk ? silu_f(to_float(row[q_off + i])) : 0.f;
     }
     for (int idx = threadIdx.x; idx < n * kLtCols; idx += kLtThreads) {
       const int tt = idx / kLtCols, j = idx - tt * kLtCols;
@@ -103,15 +111,34 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float v = vs[tt * kLtCols + col];
-      const float* kr = ks + tt * dk;
-      const float* qr = qs + tt * dk;
+      const float* kr = ks + tt * dkp;
+      const float* qr = qs + tt * dkp;
       float acc = 0.f;
+      if (KPT % 4 == 0) {
+        // four channels in a row per load: the lanes of a slice read the same 16 bytes of shared memory
 #pragma unroll
-      for (int m = 0; m < KPT; ++m) {
-        const int i = slice + 4 * m;
-        if (i < dk) {
-          S[m] = lam * S[m] + kr[i] * v;
-          if (MODE != 1) acc += S[m] * qr[i];
+        for (int m4 = 0; m4 < KPT / 4; ++m4) {
+          const int i = (slice + 4 * m4) * 4;
+          if (i < dk) {          // (channels from dk up to the row's padded end are zeros)
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+            S[4 * m4 + 0] = lam * S[4 * m4 + 0] + k4.x * v;
+            S[4 * m4 + 1] = lam * S[4 * m4 + 1] + k4.y * v;
+            S[4 * m4 + 2] = lam * S[4 * m4 + 2] + k4.z * v;
+            S[4 * m4 + 3] = lam * S[4 * m4 + 3] + k4.w * v;
+            if (MODE != 1) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+              acc += S[4 * m4 + 0] * q4.x + S[4 * m4 + 1] * q4.y + S[4 * m4 + 2] * q4.z + S[4 * m4 + 3] * q4.w;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < KPT; ++m) {
+          const int i = slice + 4 * m;
+          if (i < dk) {
+            S[m] = lam * S[m] + kr[i] * v;
+            if (MODE != 1) acc += S[m] * qr[i];
+          }
         }
       }
       if (MODE != 1) {
@@ -126,7 +153,7 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
                            : scratch + ((int64_t)blockIdx.x * H + h) * mat;
 #pragma unroll
   for (int m = 0; m < KPT; ++m) {
-    const int i = slice + 4 * m;
+    const int i = lt_channel<KPT>(slice, m);
     if (live && i < dk) dst[(int64_t)i * dv + c] = S[m];
   }
 }
@@ -186,7 +213,7 @@ template <typename T, int KPT>
 static int lightning_launch(float* out, const T* proj, int64_t ld, const float* decay, float* state, float* scratch,
                             const int* cu_q, const int* state_slots, int num_seqs, int T_rows, int H, int dk, int dv,
                             int run, int write_state, cudaStream_t stream) {
-  const size_t smem = sizeof(float) * kLtStage * (2 * dk + kLtCols);
+  const size_t smem = sizeof(float) * kLtStage * (2 * ((dk + 3) & ~3) + kLtCols);
   const int tiles = (dv + kLtCols - 1) / kLtCols;
   if (run <= 0) {      // few rows: every request is walked once
     launch_pdl(lightning_scan_kernel<T, KPT, 0>, dim3(num_seqs, H, tiles), dim3(kLtThreads), smem, stream, out, proj,
