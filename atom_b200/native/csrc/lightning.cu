@@ -115,6 +115,7 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
       const float* qr = qs + tt * dkp;
       float acc = 0.f;
       if (KPT % 4 == 0) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;      // four sums side by side: chains of KPT / 4 dependent FMAs
         // four channels in a row per load: the lanes of a slice read the same 16 bytes of shared memory
 #pragma unroll
         for (int m4 = 0; m4 < KPT / 4; ++m4) {
@@ -127,10 +128,14 @@ lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int64
             S[4 * m4 + 3] = lam * S[4 * m4 + 3] + k4.w * v;
             if (MODE != 1) {
               const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
-              acc += S[4 * m4 + 0] * q4.x + S[4 * m4 + 1] * q4.y + S[4 * m4 + 2] * q4.z + S[4 * m4 + 3] * q4.w;
+              a0 = fmaf(S[4 * m4 + 0], q4.x, a0);
+              a1 = fmaf(S[4 * m4 + 1], q4.y, a1);
+              a2 = fmaf(S[4 * m4 + 2], q4.z, a2);
+              a3 = fmaf(S[4 * m4 + 3], q4.w, a3);
             }
           }
         }
+        acc = (a0 + a1) + (a2 + a3);
       } else {
 #pragma unroll
         for (int m = 0; m < KPT; ++m) {

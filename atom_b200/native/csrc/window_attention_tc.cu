@@ -57,8 +57,14 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 __device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 a, __nv_bfloat16 b) {
   return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
 }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 // tanh(x) = 1 - 2 / (exp(2x) + 1): absolute error of a few 1e-7, exact limits at both ends.
-__device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+__device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, ex2(x * (2.f * kLog2e)) + 1.f); }
 
 // Finds request s and tile r of unit x: requests take ceil(rows / BM) units one after another.
 __device__ __forceinline__ bool find_tile(int x, const int* __restrict__ cu_q, int num_seqs, int& s, int& r) {
@@ -66,7 +72,7 @@ __device__ __forceinline__ bool find_tile(int x, const int* __restrict__ cu_q, i
   for (s = 0; s < num_seqs; ++s) {
     const int n = (cu_q[s + 1] - cu_q[s] + BM - 1) / BM;
     if (x < acc + n) {
-      r = x - acc;
+      r = n - 1 - (x - acc);          // a request's last tiles see the most keys: they start first
       return true;
     }
     acc += n;
@@ -92,24 +98,26 @@ struct Params {
   float* part;
 };
 
+// Two threads per key row: the page is looked up once per row and tile, the row's 16-byte pieces alternate between them.
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* Ks, __nv_bfloat16* Vs, const Params& p, const int* bt, int g,
                                              int j0, int p_last) {
   constexpr int KC = DK / 8, VC = DV / 8;
-  for (int idx = threadIdx.x; idx < BN * (KC + VC); idx += THREADS) {
-    const int r = idx / (KC + VC), c = idx - r * (KC + VC);
-    const int j = j0 + r;
-    int page = -1;
-    if (j <= p_last) {
-      const int lp = j / p.page_size;
-      if (lp < p.max_pages) page = bt[lp];
-    }
-    const bool valid = page >= 0 && page < p.num_pages;
-    const int64_t row = valid ? ((int64_t)page * p.nkv + g) * p.page_size + (j % p.page_size) : 0;
-    if (c < KC)
-      cp_async16(Ks + r * LDK + c * 8, p.k_pages + row * DK + c * 8, valid);
-    else
-      cp_async16(Vs + r * LDV + (c - KC) * 8, p.v_pages + row * DV + (c - KC) * 8, valid);
+  static_assert(THREADS == 2 * BN, "two threads per key row");
+  const int r = threadIdx.x >> 1, half = threadIdx.x & 1;
+  const int j = j0 + r;
+  int page = -1;
+  if (j <= p_last) {
+    const int lp = j / p.page_size;
+    if (lp < p.max_pages) page = bt[lp];
   }
+  const bool valid = page >= 0 && page < p.num_pages;
+  const int64_t row = valid ? ((int64_t)page * p.nkv + g) * p.page_size + (j % p.page_size) : 0;
+  const __nv_bfloat16* ksrc = p.k_pages + row * DK;
+  const __nv_bfloat16* vsrc = p.v_pages + row * DV;
+#pragma unroll
+  for (int c = 0; c < KC / 2; ++c) cp_async16(Ks + r * LDK + (2 * c + half) * 8, ksrc + (2 * c + half) * 8, valid);
+#pragma unroll
+  for (int c = 0; c < VC / 2; ++c) cp_async16(Vs + r * LDV + (2 * c + half) * 8, vsrc + (2 * c + half) * 8, valid);
 }
 
 __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const Params p) {
@@ -156,7 +164,9 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const bool active = warp * 16 < rows;                        // a warp without rows only helps to load
   const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
-  const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
+  // with a cap: score = cap2 * tanh(sum * in_mul); without: sum * in_mul; both in units of log 2
+  const float in_mul = p.cap > 0.f ? p.scale / p.cap : p.scale * kLog2e;
+  const float cap2 = p.cap * kLog2e;
 
   for (int i = i_begin; i < i_end; ++i) {
     const int stage = (i - i_begin) & 1;
@@ -188,22 +198,35 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
           mma_bf16(sc[2 * np + 1], a, b[2], b[3]);
         }
       }
-      // scale, cap, mask; the tile's maximum per row
-      float mx[2] = {-INFINITY, -INFINITY};
+      // scale and cap, in units of log 2 (the weights are powers of two of score differences); the mask, which only
+      // tiles at an edge need (the diagonal, the window's far end, the end of the kept tokens, a tile of few rows);
+      // the tile's maximum per row
+      const bool interior = rows == BM && j0 + BN - 1 <= p0 &&
+                            (p.window <= 0 || p_last - j0 < p.window || j0 + BN <= p.keep);
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-          const int row = (e < 2) ? row_a : row_b;
-          const int pi = p0 + row;
-          float v = sc[nt][e] * p.scale;
-          if (p.cap > 0.f) v = p.cap * tanh_fast(v * inv_cap);
-          const bool seen = row < rows && j <= pi && (p.window <= 0 || pi - j < p.window || j < p.keep);
-          v = seen ? v : -INFINITY;
-          sc[nt][e] = v;
-          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        for (int e = 0; e < 4; ++e)
+          sc[nt][e] = p.cap > 0.f ? cap2 * tanh_fast(sc[nt][e] * in_mul) : sc[nt][e] * in_mul;
+      }
+      if (!interior) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const int row = (e < 2) ? row_a : row_b;
+            const int pi = p0 + row;
+            const bool seen = row < rows && j <= pi && (p.window <= 0 || pi - j < p.window || j < p.keep);
+            if (!seen) sc[nt][e] = -INFINITY;
+          }
         }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt) {
+        mx[0] = fmaxf(mx[0], fmaxf(sc[nt][0], sc[nt][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(sc[nt][2], sc[nt][3]));
       }
       float corr[2], m_use[2];
 #pragma unroll
@@ -212,7 +235,7 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
         mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 2));
         const float m_new = fmaxf(m_run[k], mx[k]);
         m_use[k] = (m_new == -INFINITY) ? 0.f : m_new;
-        corr[k] = (m_run[k] == -INFINITY) ? 0.f : __expf(m_run[k] - m_use[k]);
+        corr[k] = (m_run[k] == -INFINITY) ? 0.f : ex2(m_run[k] - m_use[k]);
         m_run[k] = m_new;
       }
       float sum[2] = {0.f, 0.f};
@@ -222,7 +245,7 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
         __nv_bfloat16 hi[4], lw[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float pe = __expf(sc[nt][e] - m_use[e >> 1]);        // exp(-inf) = 0 for what is not seen
+          const float pe = ex2(sc[nt][e] - m_use[e >> 1]);           // 2^(-inf) = 0 for what is not seen
           sum[e >> 1] += pe;
           hi[e] = __float2bfloat16_rn(pe);
           lw[e] = __float2bfloat16_rn(pe - __bfloat162float(hi[e]));
@@ -285,7 +308,7 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
       if (row >= rows) continue;
       float* dst = p.part + ((int64_t)(t0 + row) * p.nsplit + z) * stride;
       if ((lane & 3) == 0) {
-        dst[h] = m_run[k];
+        dst[h] = m_run[k] * kLn2;                                // the merge kernel takes natural logarithms
         dst[p.nh + h] = l_run[k];
       }
       float* od = dst + 2 * p.nh + (int64_t)h * DV;
