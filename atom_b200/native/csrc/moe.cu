@@ -264,14 +264,14 @@ constexpr size_t moe_tc_smem(int bm, bool gated) {
   return sizeof(__nv_bfloat16) * kTcStages * ((size_t)bm + (gated ? 2 : 1) * kTcBN) * kTcLD;
 }
 
-template <bool GATED, bool GATHER, int BM>
+template <bool GATED, bool GATHER, int BM, int MI>
 __global__ void __launch_bounds__(kTcThreads)
 moe_gemm_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ A, int64_t lda,
                    const __nv_bfloat16* __restrict__ W, const int* __restrict__ offsets,
                    const int* __restrict__ row_token, const float* __restrict__ row_w, int E, int N, int K) {
   atom::pdl_trigger();
   atom::pdl_wait();
-  constexpr int WM = BM / 16, WN = 4 / WM;                 // warps along the rows and along the columns
+  constexpr int WM = BM / (16 * MI), WN = 4 / WM;          // warps along the rows (MI tiles of 16 rows each) and the columns
   constexpr int NT = kTcBN / WN / 8;                        // 8-column tiles of a warp
   constexpr int BROWS = (GATED ? 2 : 1) * kTcBN;
   constexpr int STAGE = (BM + BROWS) * kTcLD;
@@ -332,11 +332,14 @@ moe_gemm_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     }
   };
 
-  float g[NT][4], u[GATED ? NT : 1][4];
+  float g[MI][NT][4], u[MI][GATED ? NT : 1][4];
 #pragma unroll
-  for (int i = 0; i < NT; ++i) g[i][0] = g[i][1] = g[i][2] = g[i][3] = 0.f;
+  for (int mi = 0; mi < MI; ++mi) {
 #pragma unroll
-  for (int i = 0; i < (GATED ? NT : 1); ++i) u[i][0] = u[i][1] = u[i][2] = u[i][3] = 0.f;
+    for (int i = 0; i < NT; ++i) g[mi][i][0] = g[mi][i][1] = g[mi][i][2] = g[mi][i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < (GATED ? NT : 1); ++i) u[mi][i][0] = u[mi][i][1] = u[mi][i][2] = u[mi][i][3] = 0.f;
+  }
 
   const int steps = (K + kTcBK - 1) / kTcBK;
 #pragma unroll
@@ -353,68 +356,95 @@ moe_gemm_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     const __nv_bfloat16* Bs = As + BM * kTcLD;
 #pragma unroll
     for (int kk = 0; kk < kTcBK / 16; ++kk) {
-      uint32_t a[4];
-      moe_ldmatrix_x4(a, As + (wm * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kTcLD + kk * 16 + (lane >> 4) * 8);
+      uint32_t a[MI][4];
+#pragma unroll
+      for (int mi = 0; mi < MI; ++mi)
+        moe_ldmatrix_x4(a[mi], As + ((wm * MI + mi) * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kTcLD + kk * 16 +
+                                   (lane >> 4) * 8);
 #pragma unroll
       for (int np = 0; np < NT / 2; ++np) {
         const int brow = wn * (kTcBN / WN) + np * 16 + (lane >> 4) * 8 + (lane & 7);
         uint32_t b[4];
         moe_ldmatrix_x4(b, Bs + brow * kTcLD + kk * 16 + ((lane >> 3) & 1) * 8);
-        moe_mma_bf16(g[2 * np], a, b[0], b[1]);
-        moe_mma_bf16(g[2 * np + 1], a, b[2], b[3]);
+#pragma unroll
+        for (int mi = 0; mi < MI; ++mi) {
+          moe_mma_bf16(g[mi][2 * np], a[mi], b[0], b[1]);
+          moe_mma_bf16(g[mi][2 * np + 1], a[mi], b[2], b[3]);
+        }
         if (GATED) {
           moe_ldmatrix_x4(b, Bs + (kTcBN + brow) * kTcLD + kk * 16 + ((lane >> 3) & 1) * 8);
-          moe_mma_bf16(u[2 * np], a, b[0], b[1]);
-          moe_mma_bf16(u[2 * np + 1], a, b[2], b[3]);
+#pragma unroll
+          for (int mi = 0; mi < MI; ++mi) {
+            moe_mma_bf16(u[mi][2 * np], a[mi], b[0], b[1]);
+            moe_mma_bf16(u[mi][2 * np + 1], a[mi], b[2], b[3]);
+          }
         }
       }
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
+  for (int mi = 0; mi < MI; ++mi) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = wm * 16 + (lane >> 2) + (i >> 1) * 8;
-      const int n = n0 + wn * (kTcBN / WN) + nt * 8 + (lane & 3) * 2 + (i & 1);
-      if (r < rows && n < N) {
-        float v = g[nt][i];
-        if (GATED) {
-          // gate and up are rounded to the activation type first, as the unfused product hands them on
-          const float gr = __bfloat162float(__float2bfloat16_rn(v));
-          const float ur = __bfloat162float(__float2bfloat16_rn(u[GATED ? nt : 0][i]));
-          v = gr / (1.f + expf(-gr)) * ur;
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = (wm * MI + mi) * 16 + (lane >> 2) + (i >> 1) * 8;
+        const int n = n0 + wn * (kTcBN / WN) + nt * 8 + (lane & 3) * 2 + (i & 1);
+        if (r < rows && n < N) {
+          float v = g[mi][nt][i];
+          if (GATED) {
+            // gate and up are rounded to the activation type first, as the unfused product hands them on
+            const float gr = __bfloat162float(__float2bfloat16_rn(v));
+            const float ur = __bfloat162float(__float2bfloat16_rn(u[mi][GATED ? nt : 0][i]));
+            v = gr / (1.f + expf(-gr)) * ur;
+          }
+          out[(int64_t)(row0 + r) * N + n] = __float2bfloat16_rn(v);
         }
-        out[(int64_t)(row0 + r) * N + n] = __float2bfloat16_rn(v);
       }
     }
   }
 }
 
-template <bool GATED, bool GATHER, int BM>
-static void moe_gemm_tc_launch_one(__nv_bfloat16* out, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
+template <bool GATED, bool GATHER, int BM, int MI>
+static int moe_gemm_tc_launch_one(__nv_bfloat16* out, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                                    const int* offsets, const int* row_token, const float* row_w, int R, int E, int N,
                                    int K, cudaStream_t stream) {
   dim3 grid((R + BM - 1) / BM + E, (N + kTcBN - 1) / kTcBN);
-  launch_pdl(moe_gemm_tc_kernel<GATED, GATHER, BM>, grid, dim3(kTcThreads), moe_tc_smem(BM, GATED), stream, out, A, lda,
-             W, offsets, row_token, row_w, E, N, K);
+  constexpr size_t smem = moe_tc_smem(BM, GATED);
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(moe_gemm_tc_kernel<GATED, GATHER, BM, MI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem) != cudaSuccess)
+        return ATOM_ERR_LAUNCH;
+      attr_set = true;
+    }
+  }
+  launch_pdl(moe_gemm_tc_kernel<GATED, GATHER, BM, MI>, grid, dim3(kTcThreads), smem, stream, out, A, lda, W, offsets,
+             row_token, row_w, E, N, K);
+  return ATOM_OK;
 }
 
-// Rows per tile: 16 while the step's rows are few (decoding: an expert gets a handful), else 64.
+// Rows per tile: 16 while the step's rows are few (decoding: an expert gets a handful), else 64.  (Tiles of 128 rows,
+// a warp 32 rows so that every piece of W_e read from shared memory serves two tiles of rows, were slower: 168
+// registers a thread and 60 KB a CTA leave an SM too few warps.)
 static int moe_gemm_tc_launch(__nv_bfloat16* out, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                               const int* offsets, const int* row_token, const float* row_w, int R, int E, int N, int K,
                               int gated, int gather, cudaStream_t stream) {
   const bool small = R <= 16 * E;
-#define ATOM_MOE_TC(G, H)                                                                                       \
-  do {                                                                                                          \
-    if (small) moe_gemm_tc_launch_one<G, H, 16>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream); \
-    else moe_gemm_tc_launch_one<G, H, 64>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);       \
+  int rc = ATOM_OK;
+#define ATOM_MOE_TC(G, H)                                                                                                 \
+  do {                                                                                                                    \
+    if (small) rc = moe_gemm_tc_launch_one<G, H, 16, 1>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);   \
+    else rc = moe_gemm_tc_launch_one<G, H, 64, 1>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);         \
   } while (0)
   if (gated && gather) ATOM_MOE_TC(true, true);
   else if (gated) ATOM_MOE_TC(true, false);
   else if (gather) ATOM_MOE_TC(false, true);
   else ATOM_MOE_TC(false, false);
 #undef ATOM_MOE_TC
+  if (rc != ATOM_OK) return rc;
   return check_launch();
 }
 
