@@ -237,10 +237,11 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
 // ---- the same product in bfloat16 on the tensor cores -----------------------------------------------------------
 // A CTA of 4 warps takes BM rows of one expert (64, or 16 in steps of few rows, where the warps share out the
 // columns instead of the rows) and 64 output columns (with GATED the 64 gate rows and the 64 up rows of W_e), and
-// walks K in steps of 32: tiles of A and W_e come into shared memory with cp.async, three steps deep (gathered rows
+// walks K in steps of 32, three steps deep (of 64, four deep, with 16 rows: an expert's few rows stream its whole
+// matrix, so the bytes in flight count): tiles of A and W_e come into shared memory with cp.async (gathered rows
 // pass through registers, where they are weighted and rounded); mma.sync m16n8k16 with 32-bit sums.  Every output is
 // summed over k in the same order whatever the tile, so a row's result does not depend on the rows beside it.
-constexpr int kTcBN = 64, kTcBK = 32, kTcLD = kTcBK + 8, kTcStages = 3, kTcThreads = 128;
+constexpr int kTcBN = 64, kTcThreads = 128;
 
 __device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -260,17 +261,18 @@ __device__ __forceinline__ void moe_cp_async16(void* smem, const void* gmem, boo
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
 }
 
-constexpr size_t moe_tc_smem(int bm, bool gated) {
-  return sizeof(__nv_bfloat16) * kTcStages * ((size_t)bm + (gated ? 2 : 1) * kTcBN) * kTcLD;
+constexpr size_t moe_tc_smem(int bm, bool gated, int bk, int stages) {
+  return sizeof(__nv_bfloat16) * stages * ((size_t)bm + (gated ? 2 : 1) * kTcBN) * (bk + 8);
 }
 
-template <bool GATED, bool GATHER, int BM, int MI>
+template <bool GATED, bool GATHER, int BM, int MI, int kTcBK, int kTcStages>
 __global__ void __launch_bounds__(kTcThreads)
 moe_gemm_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ A, int64_t lda,
                    const __nv_bfloat16* __restrict__ W, const int* __restrict__ offsets,
                    const int* __restrict__ row_token, const float* __restrict__ row_w, int E, int N, int K) {
   atom::pdl_trigger();
   atom::pdl_wait();
+  constexpr int kTcLD = kTcBK + 8;                         // bf16 elements per row in shared memory
   constexpr int WM = BM / (16 * MI), WN = 4 / WM;          // warps along the rows (MI tiles of 16 rows each) and the columns
   constexpr int NT = kTcBN / WN / 8;                        // 8-column tiles of a warp
   constexpr int BROWS = (GATED ? 2 : 1) * kTcBN;
@@ -406,22 +408,22 @@ moe_gemm_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
   }
 }
 
-template <bool GATED, bool GATHER, int BM, int MI>
+template <bool GATED, bool GATHER, int BM, int MI, int BK, int STAGES>
 static int moe_gemm_tc_launch_one(__nv_bfloat16* out, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
                                    const int* offsets, const int* row_token, const float* row_w, int R, int E, int N,
                                    int K, cudaStream_t stream) {
   dim3 grid((R + BM - 1) / BM + E, (N + kTcBN - 1) / kTcBN);
-  constexpr size_t smem = moe_tc_smem(BM, GATED);
+  constexpr size_t smem = moe_tc_smem(BM, GATED, BK, STAGES);
   if (smem > 48 * 1024) {
     static bool attr_set = false;
     if (!attr_set) {
-      if (cudaFuncSetAttribute(moe_gemm_tc_kernel<GATED, GATHER, BM, MI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(moe_gemm_tc_kernel<GATED, GATHER, BM, MI, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)smem) != cudaSuccess)
         return ATOM_ERR_LAUNCH;
       attr_set = true;
     }
   }
-  launch_pdl(moe_gemm_tc_kernel<GATED, GATHER, BM, MI>, grid, dim3(kTcThreads), smem, stream, out, A, lda, W, offsets,
+  launch_pdl(moe_gemm_tc_kernel<GATED, GATHER, BM, MI, BK, STAGES>, grid, dim3(kTcThreads), smem, stream, out, A, lda, W, offsets,
              row_token, row_w, E, N, K);
   return ATOM_OK;
 }
@@ -436,8 +438,8 @@ static int moe_gemm_tc_launch(__nv_bfloat16* out, const __nv_bfloat16* A, int64_
   int rc = ATOM_OK;
 #define ATOM_MOE_TC(G, H)                                                                                                 \
   do {                                                                                                                    \
-    if (small) rc = moe_gemm_tc_launch_one<G, H, 16, 1>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);   \
-    else rc = moe_gemm_tc_launch_one<G, H, 64, 1>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);         \
+    if (small) rc = moe_gemm_tc_launch_one<G, H, 16, 1, 64, 4>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream); \
+    else rc = moe_gemm_tc_launch_one<G, H, 64, 1, 32, 3>(out, A, lda, W, offsets, row_token, row_w, R, E, N, K, stream);      \
   } while (0)
   if (gated && gather) ATOM_MOE_TC(true, true);
   else if (gated) ATOM_MOE_TC(true, false);
