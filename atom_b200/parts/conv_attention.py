@@ -80,7 +80,10 @@ class ConvWindowAttention(Mixer):
                 longest = min(step.max_ctx_len, self.window + self.keep_first) if self.window else step.max_ctx_len
                 tiles = step.num_tokens if step.max_q_len <= 1 else \
                     -(-step.num_tokens // native.WINDOW_TC_ROWS) + step.num_seqs - 1
-                plan = native.attention_mixed_splits(tiles * self.nh, longest, per_sm=2, min_share=128)
+                # (two CTAs fit an SM; steps with prompt portions fill it once before their keys are shared out: the
+                # shares cost a pass over 32-bit partial outputs of every row)
+                plan = native.attention_mixed_splits(tiles * self.nh, longest, per_sm=2 if step.max_q_len <= 1 else 1,
+                                                     min_share=128)
             else:
                 plan = 0
             step.plans[key] = plan
