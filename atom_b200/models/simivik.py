@@ -9,7 +9,7 @@ config.json:  ``architecture`` "Simivik"; ``vocab``, ``width``; ``norm.eps``;
 ``layers``: entries with ``type`` ("attention" | "lightning"), ``mixer``, ``mlp`` (or null), optional ``weights_of``.
   attention mixer: heads, kv_heads, dim, vdim, scale, softcap (absent: none), conv (taps; absent: none),
       rot {base, dims} (absent: no rotation), mask {size, keep_first} (absent: every earlier token is seen)
-  lightning mixer: heads, dim, vdim, decay (one number per head)
+  lightning mixer: heads, dim, vdim, decay (one number per head; a single number stands for all heads)
   mlp: {kind "dense", ff}  |  {kind "moe", router {experts, top}, expert {ff}, shared {ff} (absent: none)}
 
 Tensors: ``embed`` (also the output matrix), ``final.norm``, per layer ``l<i>.norm1``, ``l<i>.norm2`` and
@@ -133,6 +133,8 @@ def _attention(m: Mapping, w: str) -> AttentionMixer:
 def _lightning(m: Mapping, w: str) -> LightningMixer:
     heads = _count(m, "heads", w)
     decay = m.get("decay")
+    if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+        decay = [decay] * heads                      # one number: the same decay for every head
     if not isinstance(decay, list) or len(decay) != heads or \
             any(isinstance(v, bool) or not isinstance(v, (int, float)) for v in decay):
         raise ConfigError(f"config.json: {w}decay must list one number per head ({heads})")

@@ -41,6 +41,13 @@ def test_layers_on_anothers_tensors_have_their_own_cache():
     assert needs[1].states[0].dtype == "float32"
 
 
+def test_one_decay_for_all_heads():
+    c = copy.deepcopy(ts.CONFIGS["A"])
+    c["layers"][1]["mixer"]["decay"] = 0.75
+    c["layers"][3]["mixer"]["decay"] = 0.75
+    assert config_from_dict(c).layers[1].mixer.decay == (0.75, 0.75)
+
+
 def test_options_left_out_of_the_config():
     needs = Model(build_model_spec(config_from_dict(ts.CONFIGS["B"]))).cache_needs()
     assert needs[1].window is None and needs[1].keep_first == 0 and not needs[1].states      # no window, no convolution
