@@ -10,7 +10,7 @@ heads of 64 channels; and Mugulorn, whose layers alternate attention through a l
 128 + 64 numbers per head, values of 128, a latent of width / 4, queries through width / 2, a window of 1024;
 every second attention layer reads the cache of the one before) with a gated linear recurrence of the width's
 channels in as many blocks as heads behind a convolution of 4 taps; and Simivik, whose layers are attention behind
-a convolution of 4 taps (the same heads, all 128 numbers rotated, scores capped at 50, a window of 1024 that keeps the
+a convolution of 4 taps (the same heads, all 128 numbers rotated, scores capped at 30, a window of 1024 that keeps the
 first 64 tokens) with a dense relu-squared feed-forward, lightning attention (the same heads, 128 numbers per key and
 value) with 16 experts of the width's size of which 2 are used beside a shared one (three times the width per token,
 as the dense ones), attention with the dense feed-forward, attention with the experts, and so on.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
@@ -76,7 +76,7 @@ def mugulorn_config(width: int, heads: int, layers: int) -> dict:
 
 
 def simivik_config(width: int, heads: int, layers: int) -> dict:
-    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
            "conv": 4, "rot": {"base": 1000000.0, "dims": 128}, "mask": {"size": 1024, "keep_first": 64}}
     lin = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 7 * h / max(1, heads - 1)) for h in range(heads)]}
     dense = {"kind": "dense", "ff": 3 * width}

@@ -347,7 +347,7 @@ def test_scores_are_capped_before_the_softmax(dtype):
 
 
 TC_CASES = [  # H, G, dk, dv, window, keep, cap, page, T
-    (4, 2, 16, 32, 24, 5, 5.0, 16, 200), (8, 2, 64, 64, 128, 16, 30.0, 32, 333), (6, 3, 96, 64, 72, 70, 50.0, 16, 300),
+    (4, 2, 16, 32, 24, 5, 5.0, 16, 200), (8, 2, 64, 64, 128, 16, 30.0, 32, 333), (6, 3, 80, 48, 90, 70, 40.0, 16, 300),
     (4, 1, 128, 128, 0, 0, 0.0, 16, 270), (2, 2, 256, 16, 65, 64, 3.0, 8, 200), (3, 1, 48, 112, 1, 1, 0.0, 16, 150),
     (5, 5, 32, 80, 200, 130, 10.0, 64, 520), (16, 4, 128, 128, 100, 3, 20.0, 16, 600),
 ]
