@@ -6,7 +6,8 @@
 //                             with rows before the step's first token of a request taken from the request's
 //                             convolution state (its last taps - 1 projected rows); rotation of the first rot_dims
 //                             numbers of every query and key head by position * frequency (pairs (i, i + rot_dims/2));
-//                             q to a dense array, k and v to their pages
+//                             q to a dense array, k and v to their pages (conv_rope_write_vec_kernel: the same
+//                             for bfloat16 sizes in steps of 8, 16 bytes at a time)
 //   conv_state_update_kernel  per request: the last taps - 1 projected rows after this step
 //   window_attention_kernel   one CTA per (token, query head): keys j <= p with p - j < window or j < keep_first,
 //                             s = scale * q.k, s <- cap * tanh(s / cap), online softmax in 32-bit; any sizes, both
@@ -92,6 +93,126 @@ conv_rope_write_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, int64_t
     const int g = idx / dv, i = idx - g * dv;
     v_pages[(((int64_t)page * G + g) * page_size + slot) * dv + i] =
         from_float<T>(conv_at(qkv, ld, state_row, C, taps, conv_w, w_dtype, first, t, v0 + idx));
+  }
+}
+
+// The same in bfloat16 for sizes in steps of 8 (key and value sizes, and half of rot_dims): a thread owns 8 channels
+// in a row, so every row of inputs, the channels' taps and the outputs move 16 bytes at a time; the token's
+// convolved channels pass through shared memory in 32-bit, where a rotated pair finds its other half.  The sums run
+// over the taps in the same order as in the kernel above.
+template <int TAPS>
+__global__ void __launch_bounds__(256)
+conv_rope_write_vec_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, int64_t ld, int H,
+                           int G, int dk, int dv, const __nv_bfloat16* __restrict__ conv_w,
+                           const __nv_bfloat16* __restrict__ conv_state, const float* __restrict__ freq, int rot_dims,
+                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                           const int* __restrict__ cu_q, const int* __restrict__ state_slots,
+                           const int* __restrict__ block_table, int max_pages, int page_size,
+                           __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int64_t num_pages,
+                           int* __restrict__ status) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  extern __shared__ __align__(16) float cv_y[];      // [C]
+  const int t = blockIdx.x;
+  const int s = seq_of_token[t];
+  if (s < 0) return;
+  const int p = positions[t];
+  const int first = cu_q[s];
+  const int C = H * dk + G * dk + G * dv;
+  const __nv_bfloat16* state_row =
+      (conv_state && TAPS > 1) ? conv_state + (int64_t)state_slots[s] * (TAPS - 1) * C : nullptr;
+  const int lp = p / page_size;
+  const int page = lp < max_pages ? block_table[(int64_t)s * max_pages + lp] : -1;
+  const bool writes = k_pages != nullptr;
+  if (writes && (page < 0 || page >= num_pages)) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    return;
+  }
+  const int slot = p % page_size;
+  const int groups = C / 8;
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    const int c = g * 8;
+    float y[8];
+    if (TAPS == 0) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(qkv + (int64_t)t * ld + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        y[2 * e] = f.x;
+        y[2 * e + 1] = f.y;
+      }
+    } else {
+      constexpr int NW = TAPS > 0 ? TAPS : 1;
+      uint4 wraw[NW];                                  // the 8 channels' taps: 8 * TAPS numbers in a row
+#pragma unroll
+      for (int j = 0; j < NW; ++j) wraw[j] = *reinterpret_cast<const uint4*>(conv_w + (int64_t)c * TAPS + j * 8);
+      const __nv_bfloat16* wv = reinterpret_cast<const __nv_bfloat16*>(wraw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NW; ++j) {
+        const int tp = t - TAPS + 1 + j;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (tp >= first)
+          raw = *reinterpret_cast<const uint4*>(qkv + (int64_t)tp * ld + c);
+        else if (state_row)
+          raw = *reinterpret_cast<const uint4*>(state_row + (int64_t)(TAPS - 1 - (first - tp)) * C + c);
+        const __nv_bfloat16* xv = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] += __bfloat162float(wv[e * TAPS + j]) * __bfloat162float(xv[e]);
+      }
+    }
+    *reinterpret_cast<float4*>(cv_y + c) = make_float4(y[0], y[1], y[2], y[3]);
+    *reinterpret_cast<float4*>(cv_y + c + 4) = make_float4(y[4], y[5], y[6], y[7]);
+  }
+  __syncthreads();
+  const int half = rot_dims / 2;
+  const float pos = (float)p;
+  const int qk_end = (H + G) * dk;
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    const int c = g * 8;
+    __nv_bfloat16* dst;
+    int i0 = 0;
+    bool rotated = false;
+    if (c < qk_end) {
+      const int n = c / dk;
+      i0 = c - n * dk;
+      rotated = i0 < rot_dims;
+      if (n < H) {
+        dst = q_out + ((int64_t)t * H + n) * dk + i0;
+      } else {
+        if (!writes) continue;
+        dst = k_pages + (((int64_t)page * G + (n - H)) * page_size + slot) * dk + i0;
+      }
+    } else {
+      if (!writes) continue;
+      const int idx = c - qk_end;
+      const int gg = idx / dv;
+      dst = v_pages + (((int64_t)page * G + gg) * page_size + slot) * dv + (idx - gg * dv);
+    }
+    float o[8];
+    if (rotated) {
+      const bool low = i0 < half;                      // the first of the pair: (a, b) = (own, + half); else (- half, own)
+      const float* av = cv_y + (low ? c : c - half);
+      const float* bv = cv_y + (low ? c + half : c);
+      const float* fr = freq + (low ? i0 : i0 - half);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float sn, cs;
+        sincosf(pos * fr[e], &sn, &cs);
+        const float a = av[e], b = bv[e];
+        o[e] = low ? a * cs - b * sn : b * cs + a * sn;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = cv_y[c + e];
+    }
+    uint4 packed;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+    *reinterpret_cast<uint4*>(dst) = packed;
   }
 }
 
@@ -216,7 +337,31 @@ ATOM_EXPORT int atom_conv_rope_write(void* q_out, const void* qkv, int dtype, in
                      (const float*)qkv, ld, H, G, dk, dv, conv_w, w_dtype, taps, (const float*)conv_state, freq,
                      rot_dims, positions, seq_of_token, cu_q, state_slots, block_table, max_pages, page_size,
                      (float*)k_pages, (float*)v_pages, num_pages, status);
-  else if (dtype == ATOM_BF16)
+  else if (dtype == ATOM_BF16 && dk % 8 == 0 && dv % 8 == 0 && rot_dims % 16 == 0 && ld % 8 == 0 && taps <= 8 &&
+           (taps == 0 || w_dtype == ATOM_BF16) && ((H + 2 * G) * dk + G * dv) * sizeof(float) <= 48 * 1024 &&
+           ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)conv_w % 16) == 0 && ((uintptr_t)conv_state % 16) == 0 &&
+           ((uintptr_t)q_out % 16) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0) {
+    const int C = (H + G) * dk + G * dv;
+    const int threads = C / 8 >= 256 ? 256 : ((C / 8 + 31) / 32) * 32;
+#define ATOM_CV(TAPS)                                                                                               \
+  atom::launch_pdl(atom::conv_rope_write_vec_kernel<TAPS>, dim3(T), dim3(threads), C * sizeof(float), stream,       \
+                   (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, ld, H, G, dk, dv, (const __nv_bfloat16*)conv_w, \
+                   (const __nv_bfloat16*)conv_state, freq, rot_dims, positions, seq_of_token, cu_q, state_slots,    \
+                   block_table, max_pages, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages,  \
+                   status)
+    switch (taps) {
+      case 0: ATOM_CV(0); break;
+      case 1: ATOM_CV(1); break;
+      case 2: ATOM_CV(2); break;
+      case 3: ATOM_CV(3); break;
+      case 4: ATOM_CV(4); break;
+      case 5: ATOM_CV(5); break;
+      case 6: ATOM_CV(6); break;
+      case 7: ATOM_CV(7); break;
+      default: ATOM_CV(8); break;
+    }
+#undef ATOM_CV
+  } else if (dtype == ATOM_BF16)
     atom::launch_pdl(atom::conv_rope_write_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream,
                      (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, ld, H, G, dk, dv, conv_w, w_dtype, taps,
                      (const __nv_bfloat16*)conv_state, freq, rot_dims, positions, seq_of_token, cu_q, state_slots,

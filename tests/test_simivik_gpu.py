@@ -150,6 +150,10 @@ ATT_CASES = [  # H, G, dk, dv, taps, (base, dims), (window, keep), cap, page, le
     (4, 4, 32, 128, 3, (10000.0, 32), (64, 4), None, 16, (150, 70, 4)),
     (8, 4, 128, 128, 4, (1000000.0, 128), (50, 3), 20.0, 16, (140, 60, 10)),
     (2, 2, 80, 48, 5, (10000.0, 40), (17, 16), 4.0, 8, (64, 65, 63)),
+    (2, 2, 32, 16, None, (10000.0, 32), (20, 2), None, 8, (40, 9, 3)),
+    (4, 1, 16, 8, 1, None, None, 2.0, 8, (30, 2, 11)),
+    (2, 1, 48, 24, 8, (300.0, 16), (9, 1), 6.0, 16, (70, 20, 5)),
+    (3, 3, 24, 40, 7, (5000.0, 16), (40, 0), None, 16, (50, 33, 6)),
 ]
 
 
