@@ -88,6 +88,7 @@ _SIGNATURES = {
     "atom_conv_rope_write": [_vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i,
                              _i, _vp, _vp, _i64, _vp, _vp],
     "atom_conv_state_update": [_vp, _vp, _i, _i64, _i, _i, _vp, _vp, _i, _vp],
+    "atom_window_attention_merge": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "atom_window_attention": [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp],
     "atom_lightning_supports": [_i, _i],
     "atom_lightning_scan": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -837,7 +838,7 @@ def window_attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, 
 # ---- the same attention on the tensor cores (csrc/window_attention_tc.cu), compiled per (key size, value size) on
 # first use
 _watc_libs = {}
-_WATC_SIG = [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp, _vp]
+_WATC_SIG = [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp, _i, _vp]
 WINDOW_TC = True     # False: the plain kernel also where the tensor-core kernel takes the sizes (measurements, tests)
 WINDOW_TC_ROWS = 64  # query rows of a tile
 
@@ -871,10 +872,12 @@ def window_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tenso
                         block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                         cu_q: torch.Tensor, num_seqs: int, nh: int, nkv: int, dk: int, dv: int, scale: float,
                         softcap: float = 0.0, window: int = 0, keep_first: int = 0, nsplit: int = 1,
-                        scratch: Optional[torch.Tensor] = None) -> None:
+                        scratch: Optional[torch.Tensor] = None, heads_rows: bool = False) -> None:
     """``window_attention`` on the tensor cores: tiles of 64 consecutive tokens of a request and one head (cu_q:
     [num_seqs + 1] first token row of every request); with nsplit > 1 a tile's keys are shared out among nsplit
-    CTAs and put together by the merge kernel of ``attention_mixed``.  Sizes as ``window_attention_tc_supports``."""
+    CTAs and put together by a merge kernel.  heads_rows (only for steps in which every request brings ONE token, and
+    at most 64 query heads to a key head): a CTA's rows are the query heads of one key head for one token, so the
+    keys and values are read once per key head.  Sizes as ``window_attention_tc_supports``."""
     _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token, cu_q, scratch)
     T = q.shape[0]
     page_size = k_pages.shape[2]
@@ -885,16 +888,18 @@ def window_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tenso
     assert block_table.dtype == torch.int32 and block_table.is_contiguous()
     assert nsplit == 1 or (scratch is not None and scratch.dtype == torch.float32
                            and scratch.numel() >= attention_mixed_scratch_elems(T, nh, dv, nsplit))
-    units = -(-T // WINDOW_TC_ROWS) + num_seqs
+    assert not heads_rows or nh // nkv <= WINDOW_TC_ROWS
+    units = T if heads_rows else -(-T // WINDOW_TC_ROWS) + num_seqs
     _check(watc_lib(dk, dv).atom_window_attention_tc(
         out.data_ptr(), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
-        block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(), cu_q.data_ptr(), num_seqs, units,
-        nh, nkv, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first),
-        int(nsplit), _ptr(scratch) if nsplit > 1 else None, _stream()), "window_attention_tc")
+        block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(), seq_of_token.data_ptr(),
+        cu_q.data_ptr(), num_seqs, units, nh, nkv, float(scale), float(softcap or 0.0), int(window or 0),
+        int(keep_first), int(nsplit), _ptr(scratch) if nsplit > 1 else None, int(heads_rows), _stream()),
+        "window_attention_tc")
     if nsplit > 1:
-        _check(lib().atom_attention_mixed_merge(out.data_ptr(), dtype_code(out.dtype), scratch.data_ptr(),
-                                                seq_of_token.data_ptr(), T, nh, dv, nsplit, _stream()),
-               "attention_mixed_merge")
+        _check(lib().atom_window_attention_merge(out.data_ptr(), dtype_code(out.dtype), scratch.data_ptr(),
+                                                 seq_of_token.data_ptr(), T, nh, dv, nsplit, _stream()),
+               "window_attention_merge")
 
 
 def lightning_supports(dk: int, dv: int) -> bool:

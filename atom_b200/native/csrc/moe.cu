@@ -223,7 +223,7 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
   const int t = blockIdx.x;
   if (seq_of_token[t] < 0) return;
   const float sg = (shared_out && gate) ? 1.f / (1.f + expf(-gate[(int64_t)t * gate_ld])) : 1.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
       const int pos = pair_pos[(int64_t)t * top + k];
@@ -509,11 +509,13 @@ ATOM_EXPORT int atom_moe_combine(void* out, const void* y, int dtype, const int*
                                  const int* seq_of_token, cudaStream_t stream) {
   if (T <= 0) return ATOM_OK;
   if (n <= 0 || top <= 0) return ATOM_ERR_ARG;
+  // few rows: the columns are shared out among CTAs too (a row's sums are chains of dependent loads)
+  const dim3 grid(T, T >= 512 ? 1 : (unsigned)min(8, (n + 255) / 256));
   if (dtype == ATOM_F32)
-    atom::launch_pdl(atom::moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)y,
+    atom::launch_pdl(atom::moe_combine_kernel<float>, grid, dim3(256), 0, stream, (float*)out, (const float*)y,
                      pair_pos, pair_w, top, (const float*)shared_out, gate, gate_ld, n, seq_of_token);
   else if (dtype == ATOM_BF16)
-    atom::launch_pdl(atom::moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out,
+    atom::launch_pdl(atom::moe_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out,
                      (const __nv_bfloat16*)y, pair_pos, pair_w, top, (const __nv_bfloat16*)shared_out, gate, gate_ld, n,
                      seq_of_token);
   else

@@ -318,6 +318,31 @@ window_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   }
 }
 
+// Puts together the shares that window_attention_tc.cu left in `part`: per token and share [m (nh) | l (nh) | o (nh dv)],
+// a share's running maximum (natural logarithm), sum and unnormalised output.  One CTA per (token, head).
+template <typename T>
+__global__ void window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
+                                              const int* __restrict__ seq_of_token, int nh, int dv, int nsplit) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  if (seq_of_token[t] < 0) return;
+  const int64_t stride = (int64_t)nh * dv + 2 * nh;
+  const float* pt = part + (int64_t)t * nsplit * stride;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pt[s * stride + h]);
+  for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+    float L = 0.f, o = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m = pt[s * stride + h];
+      const float w = (m == -INFINITY) ? 0.f : expf(m - M);      // a share without keys weighs nothing
+      L = fmaf(pt[s * stride + nh + h], w, L);
+      o = fmaf(pt[s * stride + 2 * nh + (int64_t)h * dv + i], w, o);
+    }
+    out[((int64_t)t * nh + h) * dv + i] = from_float<T>(o / L);
+  }
+}
+
 }  // namespace atom
 
 // qkv: [T, >= C] rows of [q (H dk) | k (G dk) | v (G dv)], row stride ld; q_out [T, H dk] dense.  conv_w [C, taps]
@@ -408,6 +433,22 @@ ATOM_EXPORT int atom_window_attention(void* out, const void* q, int dtype, const
                      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                      (const __nv_bfloat16*)v_pages, block_table, max_pages, page_size, positions, seq_of_token, nh,
                      nkv, dk, dv, scale, softcap, window, keep_first);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
+ATOM_EXPORT int atom_window_attention_merge(void* out, int dtype, const float* part, const int* seq_of_token, int T, int nh,
+                                            int dv, int nsplit, cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (nsplit < 1 || part == nullptr || nh <= 0 || nh > 65535 || dv <= 0) return ATOM_ERR_ARG;
+  const int threads = dv >= 128 ? 128 : (dv >= 64 ? 64 : 32);
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::window_attention_merge_kernel<float>, dim3(T, nh), dim3(threads), 0, stream, (float*)out, part,
+                     seq_of_token, nh, dv, nsplit);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::window_attention_merge_kernel<__nv_bfloat16>, dim3(T, nh), dim3(threads), 0, stream,
+                     (__nv_bfloat16*)out, part, seq_of_token, nh, dv, nsplit);
   else
     return ATOM_ERR_ARG;
   return atom::check_launch();

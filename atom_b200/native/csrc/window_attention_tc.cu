@@ -10,7 +10,9 @@
 // lanes of a quad); the weights exp(s - m) enter the product with the values as TWO bfloat16 numbers, p = hi + lo,
 // so that the product sees 16 bits of their mantissa; the 16 x DV output of a warp stays in registers over all tiles.
 // With few tokens in the step the key tiles of a unit are shared out among `nsplit` CTAs, which leave maximum, sum
-// and unnormalised output per (token, head) in the scratch array of attention_mixed.cu's merge kernel.
+// and unnormalised output per (token, head) in a scratch array that window_attention.cu's merge kernel puts together.
+// In a step of single tokens a CTA's rows are the query heads that share one key head, so a request's keys and values
+// are read once per key head.
 #include "common.cuh"
 
 #if !defined(ATOM_WA_DK) || !defined(ATOM_WA_DV)
@@ -90,6 +92,7 @@ struct Params {
   int max_pages, page_size;
   int64_t num_pages;
   const int* positions;
+  const int* seq_of_token;
   const int* cu_q;
   int num_seqs, nh, nkv;
   float scale, cap;
@@ -120,6 +123,9 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* Ks, __nv_bfloat16* V
   for (int c = 0; c < VC / 2; ++c) cp_async16(Vs + r * LDV + (2 * c + half) * 8, vsrc + (2 * c + half) * 8, valid);
 }
 
+// HEADS: a step of single tokens.  A CTA's rows are the query heads of ONE key head for one token (they share the
+// keys and values, which are then read once for the group), blockIdx = (token, key head, share).
+template <bool HEADS>
 __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const Params p) {
   atom::pdl_trigger();
   atom::pdl_wait();
@@ -128,14 +134,24 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
   __nv_bfloat16* KVs = Qs + BM * LDK;                          // two stages of [K tile | V tile]
   constexpr int STAGE = BN * LDK + BN * LDV;
 
-  int s, r;
-  if (!find_tile(blockIdx.x, p.cu_q, p.num_seqs, s, r)) return;
-  const int h = blockIdx.y, z = blockIdx.z;
-  const int g = h / (p.nh / p.nkv);
-  const int t0 = p.cu_q[s] + r * BM;
-  const int rows = min(BM, p.cu_q[s + 1] - t0);
+  int s, r, h, g, t0, rows;
+  const int z = blockIdx.z;
+  if (HEADS) {
+    t0 = blockIdx.x;
+    s = p.seq_of_token[t0];
+    if (s < 0) return;
+    g = blockIdx.y;
+    rows = p.nh / p.nkv;
+    h = g * rows;                                               // the group's first head; row r is head h + r
+  } else {
+    if (!find_tile(blockIdx.x, p.cu_q, p.num_seqs, s, r)) return;
+    h = blockIdx.y;
+    g = h / (p.nh / p.nkv);
+    t0 = p.cu_q[s] + r * BM;
+    rows = min(BM, p.cu_q[s + 1] - t0);
+  }
   const int p0 = p.positions[t0];
-  const int p_last = p0 + rows - 1;
+  const int p_last = HEADS ? p0 : p0 + rows - 1;
   const int* bt = p.block_table + (int64_t)s * p.max_pages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -153,7 +169,8 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
   for (int idx = threadIdx.x; idx < BM * KC; idx += THREADS) {
     const int rr = idx / KC, c = idx - rr * KC;
     const bool valid = rr < rows;
-    cp_async16(Qs + rr * LDK + c * 8, p.q + (int64_t)(t0 + (valid ? rr : 0)) * p.q_stride + (int64_t)h * DK + c * 8, valid);
+    const int qt = HEADS ? t0 : t0 + (valid ? rr : 0), qh = HEADS ? h + (valid ? rr : 0) : h;
+    cp_async16(Qs + rr * LDK + c * 8, p.q + (int64_t)qt * p.q_stride + (int64_t)qh * DK + c * 8, valid);
   }
   if (i_begin < i_end) load_kv_tile(KVs, KVs + BN * LDK, p, bt, g, tile_of(i_begin) * BN, p_last);
   cp_async_commit();
@@ -201,7 +218,7 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
       // scale and cap, in units of log 2 (the weights are powers of two of score differences); the mask, which only
       // tiles at an edge need (the diagonal, the window's far end, the end of the kept tokens, a tile of few rows);
       // the tile's maximum per row
-      const bool interior = rows == BM && j0 + BN - 1 <= p0 &&
+      const bool interior = !HEADS && rows == BM && j0 + BN - 1 <= p0 &&
                             (p.window <= 0 || p_last - j0 < p.window || j0 + BN <= p.keep);
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) {
@@ -216,7 +233,7 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
           for (int e = 0; e < 4; ++e) {
             const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
             const int row = (e < 2) ? row_a : row_b;
-            const int pi = p0 + row;
+            const int pi = HEADS ? p0 : p0 + row;
             const bool seen = row < rows && j <= pi && (p.window <= 0 || pi - j < p.window || j < p.keep);
             if (!seen) sc[nt][e] = -INFINITY;
           }
@@ -294,7 +311,7 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
       const int row = k ? row_b : row_a;
       if (row >= rows) continue;
       const float inv = l_run[k] > 0.f ? 1.f / l_run[k] : 0.f;
-      __nv_bfloat16* dst = p.out + (int64_t)(t0 + row) * p.nh * DV + (int64_t)h * DV;
+      __nv_bfloat16* dst = p.out + (int64_t)(HEADS ? t0 : t0 + row) * p.nh * DV + (int64_t)(HEADS ? h + row : h) * DV;
 #pragma unroll
       for (int nt = 0; nt < DV / 8; ++nt)
         *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + col) =
@@ -306,12 +323,13 @@ __global__ void __launch_bounds__(THREADS, 2) window_attention_tc_kernel(const P
     for (int k = 0; k < 2; ++k) {
       const int row = k ? row_b : row_a;
       if (row >= rows) continue;
-      float* dst = p.part + ((int64_t)(t0 + row) * p.nsplit + z) * stride;
+      float* dst = p.part + ((int64_t)(HEADS ? t0 : t0 + row) * p.nsplit + z) * stride;
+      const int hh = HEADS ? h + row : h;
       if ((lane & 3) == 0) {
-        dst[h] = m_run[k] * kLn2;                                // the merge kernel takes natural logarithms
-        dst[p.nh + h] = l_run[k];
+        dst[hh] = m_run[k] * kLn2;                               // the merge kernel takes natural logarithms
+        dst[p.nh + hh] = l_run[k];
       }
-      float* od = dst + 2 * p.nh + (int64_t)h * DV;
+      float* od = dst + 2 * p.nh + (int64_t)hh * DV;
 #pragma unroll
       for (int nt = 0; nt < DV / 8; ++nt)
         *reinterpret_cast<float2*>(od + nt * 8 + col) = make_float2(o[nt][2 * k], o[nt][2 * k + 1]);
@@ -328,17 +346,18 @@ ATOM_EXPORT void atom_watc_sizes(int* dk, int* dv) {
 }
 
 // out [T, nh * DV]; q: row t at q + t * q_stride, heads packed [nh, DK]; k_pages [pages, nkv, page, DK]; v_pages
-// [pages, nkv, page, DV]; units: an upper bound of the step's tiles (ceil(T / 64) + num_seqs).  nsplit > 1: part holds
+// [pages, nkv, page, DV]; units: an upper bound of the step's tiles (ceil(T / 64) + num_seqs), or with heads_rows (a
+// step of single tokens: a CTA's rows are the query heads of one key head) the step's tokens.  nsplit > 1: part holds
 // T * nsplit * nh * (DV + 2) floats, which attention_mixed.cu's merge kernel puts together.
 ATOM_EXPORT int atom_window_attention_tc(void* out, const void* q, int64_t q_stride, const void* k_pages,
                                          const void* v_pages, int64_t num_pages, const int* block_table, int max_pages,
-                                         int page_size, const int* positions, const int* cu_q, int num_seqs, int units,
-                                         int nh, int nkv, float scale, float cap, int window, int keep, int nsplit,
-                                         float* part, cudaStream_t stream) {
+                                         int page_size, const int* positions, const int* seq_of_token, const int* cu_q,
+                                         int num_seqs, int units, int nh, int nkv, float scale, float cap, int window,
+                                         int keep, int nsplit, float* part, int heads_rows, cudaStream_t stream) {
   using namespace atom::watc;
   if (units <= 0) return ATOM_OK;
   if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || nsplit < 1 || nsplit > 65535 || nh > 65535 ||
-      (nsplit > 1 && part == nullptr) || (q_stride % 8) != 0)
+      (nsplit > 1 && part == nullptr) || (q_stride % 8) != 0 || (heads_rows && nh / nkv > BM))
     return ATOM_ERR_ARG;
   Params p;
   p.out = (__nv_bfloat16*)out;
@@ -351,6 +370,7 @@ ATOM_EXPORT int atom_window_attention_tc(void* out, const void* q, int64_t q_str
   p.page_size = page_size;
   p.num_pages = num_pages;
   p.positions = positions;
+  p.seq_of_token = seq_of_token;
   p.cu_q = cu_q;
   p.num_seqs = num_seqs;
   p.nh = nh;
@@ -363,11 +383,16 @@ ATOM_EXPORT int atom_window_attention_tc(void* out, const void* q, int64_t q_str
   p.part = part;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(window_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(window_attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(window_attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kSmemBytes) != cudaSuccess)
       return ATOM_ERR_LAUNCH;
     attr_set = true;
   }
-  atom::launch_pdl(window_attention_tc_kernel, dim3(units, nh, nsplit), dim3(THREADS), kSmemBytes, stream, p);
+  if (heads_rows)      // units: the step's tokens
+    atom::launch_pdl(window_attention_tc_kernel<true>, dim3(units, nkv, nsplit), dim3(THREADS), kSmemBytes, stream, p);
+  else
+    atom::launch_pdl(window_attention_tc_kernel<false>, dim3(units, nh, nsplit), dim3(THREADS), kSmemBytes, stream, p);
   return atom::check_launch();
 }

@@ -70,22 +70,28 @@ class ConvWindowAttention(Mixer):
                          states=states)
 
     def launch_plan(self, step):
-        """Into how many shares the tensor-core kernel cuts the key tiles of every (tile of 64 tokens, head), or 0 for
-        the plain kernel.  Where the tiles do not fill the device (decoding, short portions) their keys are shared
-        out, in shares of at least 128."""
-        key = ("conv_window_attention", self.nh, self.dk, self.dv, self.window or 0, self.keep_first)
+        """(into how many shares the tensor-core kernel cuts the key tiles of every unit, or 0 for the plain kernel;
+        whether a unit is a token with the query heads of one key head as rows, which steps of single tokens use, or
+        a tile of 64 tokens with one head).  Where the units do not fill the device (decoding, short portions) their
+        keys are shared out, in shares of at least 128."""
+        key = ("conv_window_attention", self.nh, self.nkv, self.dk, self.dv, self.window or 0, self.keep_first)
         plan = step.plans.get(key)
         if plan is None:
             if native.WINDOW_TC and native.window_attention_tc_supports(self.dk, self.dv, self.rt.dtype):
                 longest = min(step.max_ctx_len, self.window + self.keep_first) if self.window else step.max_ctx_len
-                tiles = step.num_tokens if step.max_q_len <= 1 else \
-                    -(-step.num_tokens // native.WINDOW_TC_ROWS) + step.num_seqs - 1
+                heads_rows = step.max_q_len <= 1 and self.nh // self.nkv <= native.WINDOW_TC_ROWS
+                if heads_rows:
+                    units = step.num_tokens * self.nkv
+                elif step.max_q_len <= 1:
+                    units = step.num_tokens * self.nh
+                else:
+                    units = (-(-step.num_tokens // native.WINDOW_TC_ROWS) + step.num_seqs - 1) * self.nh
                 # (two CTAs fit an SM; steps with prompt portions fill it once before their keys are shared out: the
                 # shares cost a pass over 32-bit partial outputs of every row)
-                plan = native.attention_mixed_splits(tiles * self.nh, longest, per_sm=2 if step.max_q_len <= 1 else 1,
-                                                     min_share=128)
+                plan = (native.attention_mixed_splits(units, longest, per_sm=2 if step.max_q_len <= 1 else 1,
+                                                      min_share=128), heads_rows)
             else:
-                plan = 0
+                plan = (0, False)
             step.plans[key] = plan
         return plan
 
@@ -107,14 +113,14 @@ class ConvWindowAttention(Mixer):
         if conv_state is not None and writes_cache:
             native.conv_state_update(conv_state, qkv, step.cu_q, step.state_slots, step.num_seqs)
         o = ws.get("cwa.o", (T, nh * dv), dt)
-        nsplit = self.launch_plan(step)
+        nsplit, heads_rows = self.launch_plan(step)
         if nsplit:
             scratch = None
             if nsplit > 1:
                 scratch = ws.get("cwa.splits", (native.attention_mixed_scratch_elems(T, nh, dv, nsplit),), torch.float32)
             native.window_attention_tc(o, q, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token,
                                        step.cu_q, step.num_seqs, nh, nkv, dk, dv, self.scale, self.softcap,
-                                       self.window or 0, self.keep_first, nsplit, scratch)
+                                       self.window or 0, self.keep_first, nsplit, scratch, heads_rows)
         else:
             native.window_attention(o, q, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token, nh, nkv,
                                     dk, dv, self.scale, self.softcap, self.window or 0, self.keep_first)

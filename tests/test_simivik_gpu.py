@@ -259,8 +259,9 @@ def _run_window_attention(q, k, v, scale, cap, window, keep, dtype, page, cuts, 
             ns = int(kernel[2:])
             scratch = torch.full((native.attention_mixed_scratch_elems(n, H, dv, ns),), float("nan"), dtype=torch.float32,
                                  device=DEV) if ns > 1 else None
+            # (a step of one token also runs the form whose rows are the query heads of a key head)
             native.window_attention_tc(o, qd, kp, vp, table, _i32(range(at, at + n)), _i32([0] * n), _i32([0, n]), 1, H, G,
-                                       dk, dv, scale, cap, window, keep, ns, scratch)
+                                       dk, dv, scale, cap, window, keep, ns, scratch, heads_rows=(n == 1 and at % 2 == 0))
         else:
             native.window_attention(o, qd, kp, vp, table, _i32(range(at, at + n)), _i32([0] * n), H, G, dk, dv, scale,
                                     cap, window, keep)
