@@ -7,7 +7,7 @@ its own.
 
 config.json:  ``architecture`` "Simivik"; ``vocab``, ``width``; ``norm.eps``;
 ``layers``: entries with ``type`` ("attention" | "lightning"), ``mixer``, ``mlp`` (or null), optional ``weights_of``.
-  attention mixer: heads, kv_heads, dim, vdim, scale, softcap (absent: none), conv (taps; absent: none),
+  attention mixer: heads, kv_heads, dim, vdim, scale, softcap (absent or 0: none), conv (taps; absent or 0: none),
       rot {base, dims} (absent: no rotation), mask {size, keep_first} (absent: every earlier token is seen)
   lightning mixer: heads, dim, vdim, decay (one number per head; a single number stands for all heads)
   mlp: {kind "dense", ff}  |  {kind "moe", router {experts, top}, expert {ff}, shared {ff} (absent: none)}
@@ -117,9 +117,11 @@ def _attention(m: Mapping, w: str) -> AttentionMixer:
     cap = m.get("softcap")
     if cap is not None:
         cap = _number(m, "softcap", w)
-        if cap <= 0:
+        if cap < 0:
             raise ConfigError(f"config.json: {w}softcap must be positive, got {cap}")
-    taps = _count(m, "conv", w) if m.get("conv") is not None else None
+        cap = cap or None                            # (0 stands for no cap, as an absent key does)
+    taps = _count(m, "conv", w, 0) if m.get("conv") is not None else None
+    taps = taps or None                              # (0 taps: no convolution)
     out = AttentionMixer(heads=_count(m, "heads", w), kv_heads=_count(m, "kv_heads", w), dim=_count(m, "dim", w),
                          vdim=_count(m, "vdim", w), scale=_number(m, "scale", w), softcap=cap, taps=taps,
                          rot_base=base, rot_dims=dims, window=window, keep_first=keep)

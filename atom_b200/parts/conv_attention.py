@@ -45,7 +45,9 @@ class ConvWindowAttention(Mixer):
             raise ValueError(f"conv_window_attention: value_dim {value_dim} is beyond what the kernels take (512)")
         self.hidden_size, self.nh, self.nkv, self.dk, self.dv = hidden_size, num_heads, num_kv_heads, key_dim, value_dim
         self.scale, self.softcap, self.taps = float(scale), (float(softcap) if softcap else 0.0), taps
-        self.window, self.keep_first = (int(window) if window else None), (int(keep_first) if window else 0)
+        # (a window beyond any context is one that never closes; the kernels take 32-bit sizes)
+        self.window = min(int(window), 1 << 30) if window else None
+        self.keep_first = min(int(keep_first), 1 << 30) if window else 0
         self.position = registry.build("position", position) if position is not None else None
         if self.position is not None and not hasattr(self.position, "frequencies"):
             raise ValueError("conv_window_attention rotates by frequencies (a position part with ``frequencies``)")

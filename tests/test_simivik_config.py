@@ -48,6 +48,17 @@ def test_one_decay_for_all_heads():
     assert config_from_dict(c).layers[1].mixer.decay == (0.75, 0.75)
 
 
+def test_zero_stands_for_an_option_left_out():
+    c = copy.deepcopy(ts.CONFIGS["B"])
+    m = c["layers"][2]["mixer"]
+    m.update(softcap=0, conv=0)
+    m["rot"]["dims"] = 0
+    layer = config_from_dict(c).layers[2]
+    assert layer.mixer.softcap is None and layer.mixer.taps is None and layer.mixer.rot_dims == 0
+    spec = build_model_spec(config_from_dict(c))
+    assert spec.layers[2].parts["mixer"].args["position"] is None and spec.layers[2].parts["mixer"].args["taps"] is None
+
+
 def test_options_left_out_of_the_config():
     needs = Model(build_model_spec(config_from_dict(ts.CONFIGS["B"]))).cache_needs()
     assert needs[1].window is None and needs[1].keep_first == 0 and not needs[1].states      # no window, no convolution
@@ -69,7 +80,7 @@ def test_options_left_out_of_the_config():
     (lambda c: c["layers"][1]["mlp"]["router"].update(top=7), "router.top"),
     (lambda c: c["layers"][0]["mlp"].update(kind="experts"), "mlp.kind"),
     (lambda c: c["layers"][0]["mixer"].pop("scale"), "scale"),
-    (lambda c: c["layers"][0]["mixer"].update(softcap=0), "softcap"),
+    (lambda c: c["layers"][0]["mixer"].update(softcap=-1.0), "softcap"),
     (lambda c: c["layers"][0]["mixer"]["mask"].update(size=0), "mask.'size'"),
     (lambda c: c["norm"].pop("eps"), "eps"),
 ])
