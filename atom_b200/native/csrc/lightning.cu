@@ -183,12 +183,22 @@ __global__ void lightning_prefix_kernel(float* __restrict__ state, float* __rest
   const float lam_run = powf(lam, (float)run);
   float* st = state + ((int64_t)state_slots[s] * H + h) * mat + e;
   float S = *st;
-  for (int r = 0; r < n_runs; ++r) {
-    float* b = scratch + ((int64_t)(slot0 + r) * H + h) * mat + e;
-    const float sum = *b;
-    *b = S;
-    const int rl = min(run, len - r * run);
-    S = (rl == run ? lam_run : powf(lam, (float)rl)) * S + sum;
+  // the runs' sums do not depend on S: sixteen loads are under way together before the chain of updates uses them
+  constexpr int kAhead = 16;
+  for (int r0 = 0; r0 < n_runs; r0 += kAhead) {
+    float sums[kAhead];
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j)
+      sums[j] = (r0 + j < n_runs) ? scratch[((int64_t)(slot0 + r0 + j) * H + h) * mat + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) {
+      const int r = r0 + j;
+      if (r < n_runs) {
+        scratch[((int64_t)(slot0 + r) * H + h) * mat + e] = S;
+        const int rl = min(run, len - r * run);
+        S = (rl == run ? lam_run : powf(lam, (float)rl)) * S + sums[j];
+      }
+    }
   }
   if (write_state) *st = S;
 }
