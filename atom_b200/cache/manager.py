@@ -6,7 +6,9 @@ keeps: (the arrays it holds per token, window).  A group has its own pool and it
 per request; all slots of a group share the table (page id p means page p of every slot's
 storage in that group).  A group with a window gives pages back as soon as every position
 on them is further back than any later query can look; the pages of the first ``keep_first``
-positions, which every later query still sees, stay.
+positions, which every later query still sees, stay.  A need that also keeps one row per whole block of
+positions (``CacheNeed.block_entries``) gets a second group for those rows: its pages hold ``page_size`` rows, a
+request of n positions has n // block of them, and no window gives them back.
 
 Accounting per request, in tokens:
   extend(id, n)   make room for positions [0, n): takes pages, may raise OutOfPages
@@ -45,6 +47,7 @@ class CacheGroup:
     entries: Tuple                   # the CacheEntry arrays every slot of the group holds per token
     slots: List[int]                 # cache slots (run-order cache ids) stored in this group
     pool: PagePool = None            # type: ignore
+    block: int = 0                   # > 0: the group holds one row per whole block of this many positions
 
 
 @dataclass
@@ -72,6 +75,7 @@ class CacheManager:
         self.prefix_query_tokens = 0             # tokens of the requests that were looked up
         self.groups: List[CacheGroup] = []
         self.slot_group: Dict[int, int] = {}
+        self.slot_block_group: Dict[int, int] = {}     # cache slot -> the group of its rows per block, if it keeps any
         self.state_needs: Dict[int, CacheNeed] = {}
         by_key: Dict[Tuple, CacheGroup] = {}
         for slot in sorted(needs):
@@ -94,6 +98,19 @@ class CacheManager:
                 self.groups.append(g)
             g.slots.append(slot)
             self.slot_group[slot] = g.index
+            k = need.block_group_key()
+            if k is not None:
+                g = by_key.get(k)
+                if g is None:
+                    g = CacheGroup(len(self.groups), k, None, 0, need.block_entries, [], block=need.block)
+                    # (rows of whole blocks only: a request's pages in a token group, divided by the block's length
+                    # and rounded up, bound its pages here)
+                    n = num_pages[k] if isinstance(num_pages, dict) else -(-num_pages // need.block) + max_requests
+                    g.pool = PagePool(n)
+                    by_key[k] = g
+                    self.groups.append(g)
+                g.slots.append(slot)
+                self.slot_block_group[slot] = g.index
         self.state_slots = StateSlots(max_requests)
         self.admit_hooks = []                    # called with the state slot of every request that is admitted
         self.requests: Dict[Hashable, RequestCache] = {}
@@ -110,6 +127,11 @@ class CacheManager:
         first_pos = committed - g.window + 1   # oldest key the next query (at `committed`) sees
         return max(0, first_pos) // self.page_size
 
+    def _logical_pages(self, g: CacheGroup, n_tokens: int) -> int:
+        """Pages of the group that positions [0, n_tokens) of a request reach into."""
+        rows = n_tokens // g.block if g.block else n_tokens
+        return -(-rows // self.page_size)
+
     def _kept_pages(self, g: CacheGroup) -> int:
         """Leading logical pages that hold one of the first positions a window never drops."""
         return -(-g.keep_first // self.page_size) if g.window is not None else 0
@@ -118,8 +140,8 @@ class CacheManager:
         """Pages each group must give so that positions [0, n_tokens) of the request are held."""
         rc = self.requests.get(rid) if rid is not None else None
         out = {}
-        n_logical = -(-n_tokens // self.page_size)
         for g in self.groups:
+            n_logical = self._logical_pages(g, n_tokens)
             if rc is None:
                 out[g.index] = n_logical - self._first_needed_page(g, 0)
             else:
@@ -138,9 +160,9 @@ class CacheManager:
         """Most pages a request of n_tokens holds at once in each group, when no step brings
         more than max_portion of its tokens: all of them without a window, else the portion
         plus the window (and the partial pages at both ends)."""
-        n_logical = -(-n_tokens // self.page_size)
         out = {}
         for g in self.groups:
+            n_logical = self._logical_pages(g, n_tokens)
             if g.window is None:
                 out[g.index] = n_logical
             else:
@@ -197,7 +219,7 @@ class CacheManager:
         if n_tokens < rc.committed:
             raise ValueError(f"request {rid!r}: commit({n_tokens}) below what is committed")
         for g in self.groups:
-            if n_tokens > len(rc.tables[g.index]) * self.page_size:
+            if self._logical_pages(g, n_tokens) > len(rc.tables[g.index]):
                 raise ValueError(f"request {rid!r}: commit({n_tokens}) beyond what was reserved")
         rc.committed = n_tokens
         for g in self.groups:

@@ -23,12 +23,17 @@ class CacheView:
     pages: Dict[str, torch.Tensor] = field(default_factory=dict)   # entry name -> [pages, ..., page size, last]
     state: Optional[torch.Tensor] = None     # [state slots, *shape]: the array of a need of kind "state" with a shape
     states: Dict[str, torch.Tensor] = field(default_factory=dict)  # named state arrays, each [state slots, *shape]
+    # rows kept per whole block of positions (CacheNeed.block_entries): their page group and arrays, a row where a
+    # token group has a token
+    block_group: int = -1
+    block_pages: Dict[str, torch.Tensor] = field(default_factory=dict)
 
     def member(self, name: str) -> "CacheView":
         """The view of one member of a mixer whose need was put together with ``CacheNeed.merged``: the pages,
         and the state arrays ``<name>.<array>`` under their own names (``<name>.state`` as ``state``)."""
         own = {k[len(name) + 1:]: v for k, v in self.states.items() if k.startswith(name + ".")}
-        return CacheView(self.slot, self.group, self.page_size, self.pages, own.pop("state", None), own)
+        return CacheView(self.slot, self.group, self.page_size, self.pages, own.pop("state", None), own,
+                         self.block_group, self.block_pages)
 
     @property
     def k_pages(self) -> Optional[torch.Tensor]:   # [pages, kv heads, page size, head size]
@@ -62,7 +67,11 @@ class CacheStorage:
                 self.arrays.append(a)
                 per_entry[e.name] = a
             for i, slot in enumerate(g.slots):
-                self._views[slot] = CacheView(slot, g.index, ps, {n: a[i] for n, a in per_entry.items()})
+                if g.block:        # (the slot's token group stands before it in the list: its view exists)
+                    self._views[slot].block_group = g.index
+                    self._views[slot].block_pages = {n: a[i] for n, a in per_entry.items()}
+                else:
+                    self._views[slot] = CacheView(slot, g.index, ps, {n: a[i] for n, a in per_entry.items()})
         n_slots = manager.state_slots.num_slots
         for slot, need in manager.state_needs.items():
             view = self._views.get(slot)
@@ -106,5 +115,6 @@ class CacheStorage:
                 n = manager.page_size
                 for d in e.shape:
                     n *= d
-                total += len(g.slots) * n * torch.empty((), dtype=_entry_dtype(e, dtype)).element_size()
+                b = len(g.slots) * n * torch.empty((), dtype=_entry_dtype(e, dtype)).element_size()
+                total += -(-b // g.block) if g.block else b
         return total

@@ -8,7 +8,7 @@ def _load_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from . import mugulorn, nurinex, qwen3, simivik  # noqa: F401
+        from . import kibotar, mugulorn, nurinex, qwen3, simivik  # noqa: F401
 
 
 from .registry import (  # noqa: E402

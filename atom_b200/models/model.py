@@ -13,8 +13,12 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
 from ..parts import registry
 from ..parts.base import Part, Runtime
-from ..parts.linear import resolve
+from ..parts.linear import NormedDelta, resolve
 from ..parts.spec import CacheNeed, ModelSpec, PartSpec
+
+
+# The cache slot of an embedding that keeps something per request (``cache_need`` as a mixer's).
+EMBEDDING_CACHE = -1
 
 
 class Model:
@@ -34,13 +38,22 @@ class Model:
             built = {n: registry.build(slots[n], ls.parts[n]) for n in slots if n in ls.parts}
             self.blocks.append(arrangement(**built, **dict(ls.args)))
             self._named += [(f"layers.{i}.{n}", built[n], ls.parts[n]) for n in slots if n in built]
+        self.stream_steps = None
+        if spec.stream_steps is not None:
+            self.stream_steps = registry.build("stream", spec.stream_steps)
+            self._named.append(("stream_steps", self.stream_steps, spec.stream_steps))
         self.final_norm = registry.build("norm", spec.final_norm)
         self.lm_head = registry.build("head", spec.lm_head)
         self._named += [("final_norm", self.final_norm, spec.final_norm), ("lm_head", self.lm_head, spec.lm_head)]
         for e in spec.run_order:
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"run order names layer {e.layer}, the model has {len(self.blocks)}")
+            if e.add_step is not None and (self.stream_steps is None or not 0 <= e.add_step < self.stream_steps.count):
+                raise ValueError(f"run order adds step vector {e.add_step}, which the model does not have")
+            if e.cache == EMBEDDING_CACHE:
+                raise ValueError(f"cache slot {EMBEDDING_CACHE} belongs to the embedding")
         self.rt: Optional[Runtime] = None
+        self.cache_slots = frozenset(self.cache_needs())
 
     # ------------------------------------------------------------------ description
 
@@ -56,6 +69,10 @@ class Model:
         """Cache slot -> what the mixers that run on it keep there."""
         needs: Dict[int, CacheNeed] = {}
         writers: Dict[int, int] = {}
+        own = getattr(self.embedding, "cache_need", None)
+        if own is not None and own() is not None:
+            needs[EMBEDDING_CACHE] = own()
+            writers[EMBEDDING_CACHE] = 1
         for e in self.spec.run_order:
             mixer = getattr(self.blocks[e.layer], "mixer", None)   # a layer may have none
             need = mixer.cache_need() if mixer is not None else None
@@ -101,11 +118,16 @@ class Model:
 
     def forward(self, step, caches) -> torch.Tensor:
         """step: StepContext; caches: cache slot -> CacheView.  Returns [R, vocab] float32."""
-        residual = self.embedding.forward(step.token_ids, step.num_tokens)
+        if EMBEDDING_CACHE in self.cache_slots:
+            residual = self.embedding.forward(step.token_ids, step.num_tokens, step, caches.get(EMBEDDING_CACHE))
+        else:
+            residual = self.embedding.forward(step.token_ids, step.num_tokens)
         delta = None
         scale = 1.0      # the factor with which the pending delta enters the residual (a block's ``delta_scale``)
         for e in self.spec.run_order:
             block = self.blocks[e.layer]
+            if e.add_step is not None:
+                self.stream_steps.add(residual, e.add_step)     # (sums commute: the pending delta is added by the next norm)
             if not getattr(block, "takes_pending", False):
                 delta = resolve(delta)      # (a block may hand its last product on unrun)
             if scale != 1.0 and delta is not None:
@@ -116,7 +138,9 @@ class Model:
             else:
                 delta = block.run(residual, delta, step, caches.get(e.cache), e.writes_cache)
             scale = getattr(block, "delta_scale", 1.0)
-        if scale != 1.0:
+        if isinstance(delta, NormedDelta) and getattr(self.final_norm, "fuses_products", False) and scale == 1.0:
+            y = self.final_norm.add_norm(residual, delta, "norm.final", step.logits_rows, step.num_logits_rows)
+        elif scale != 1.0:
             y = self.final_norm.add_norm(residual, resolve(delta), "norm.final", step.logits_rows,
                                          step.num_logits_rows, delta_scale=scale)
         else:

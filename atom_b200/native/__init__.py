@@ -58,6 +58,18 @@ _vp, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c
 
 _SIGNATURES = {
     "atom_embedding": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
+    "atom_pair_embedding": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _f, _i, _vp],
+    "atom_add_row": [_vp, _vp, _i, _i, _i, _vp],
+    "atom_normed_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _f, _vp, _i, _f, _vp, _i, _i, _vp],
+    "atom_head_gate": [_vp, _vp, _i, _i64, _i, _i, _i, _vp],
+    "atom_gla_supports": [_i, _i],
+    "atom_gla_scan": [_vp, _vp, _vp, _vp, _i, _i64, _vp, _i64, _vp, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                      _i, _i, _i, _vp],
+    "atom_gla_gate_norm": [_vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _f, _vp, _vp],
+    "atom_pooled_attention_supports": [_i, _i, _i, _i],
+    "atom_pool_blocks": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "atom_pooled_attention": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i,
+                              _f, _i, _i, _i, _vp, _vp, _i64, _vp],
     "atom_xielu": [_vp, _vp, _i, _i64, _f, _f, _vp],
     "atom_tanh": [_vp, _i, _i64, _vp],
     "atom_pair_rmsnorm_add": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
@@ -597,24 +609,28 @@ def gemm_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
                                         ws.numel(), _stream()), "gemm_bf16_batched", own=False)
 
 
-def latent_prepare(cq: torch.Tensor, proj: torch.Tensor, q_off: int, wq: torch.Tensor, eps: float,
+def latent_prepare(cq: Optional[torch.Tensor], proj: torch.Tensor, q_off: int, wq: Optional[torch.Tensor], eps: float,
                    positions: torch.Tensor, seq_of_token: torch.Tensor, kv_off: int = 0, kv_rank: int = 0,
                    rot_dim: int = 0, rot_dims: int = 0, wkv: Optional[torch.Tensor] = None,
                    freq: Optional[torch.Tensor] = None, mag: float = 1.0, block_table: Optional[torch.Tensor] = None,
                    page_size: int = 0, pages: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
     """Per token: cq = rmsnorm(proj[:, q_off : q_off + Rq]; wq); with ``pages``, the row [rmsnorm(first kv_rank
     numbers at kv_off; wkv) | the next rot_dim numbers, the first rot_dims of them rotated by position * freq and
-    scaled by mag] goes to the token's place in the pages [pages, page size, kv_rank + rot_dim]."""
+    scaled by mag] goes to the token's place in the pages [pages, page size, kv_rank + rot_dim].  cq None: only the
+    page row is made (queries that pass no latent of their own)."""
     _cuda(cq, proj, wq, positions, seq_of_token, wkv, freq, block_table, pages, status)
-    T, Rq = cq.shape
-    assert proj.stride(1) == 1 and proj.dtype == cq.dtype and cq.is_contiguous() and wq.numel() == Rq
+    T, Rq = (cq.shape if cq is not None else (proj.shape[0], 0))
+    assert proj.stride(1) == 1
+    assert cq is None or (proj.dtype == cq.dtype and cq.is_contiguous() and wq.numel() == Rq)
     if pages is not None:
         assert pages.dtype == proj.dtype and pages.is_contiguous() and tuple(pages.shape[1:]) == (page_size, kv_rank + rot_dim)
-        assert wkv.numel() == kv_rank and wkv.dtype == wq.dtype and freq.dtype == torch.float32 and freq.numel() >= rot_dims // 2
+        assert wkv.numel() == kv_rank and (wq is None or wkv.dtype == wq.dtype)
+        assert rot_dims == 0 or (freq.dtype == torch.float32 and freq.numel() >= rot_dims // 2)
         assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
     _check(lib().atom_latent_prepare(
-        cq.data_ptr(), proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), q_off, Rq, wq.data_ptr(), kv_off,
-        kv_rank, rot_dim, rot_dims, _ptr(wkv), dtype_code(wq.dtype), float(eps), _ptr(freq), float(mag),
+        _ptr(cq), proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), q_off, Rq, _ptr(wq), kv_off,
+        kv_rank, rot_dim, rot_dims, _ptr(wkv), dtype_code((wq if wq is not None else wkv).dtype), float(eps), _ptr(freq),
+        float(mag),
         positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table),
         block_table.shape[1] if block_table is not None else 0, page_size, _ptr(pages),
         pages.shape[0] if pages is not None else 0, _ptr(status), T, _stream()), "latent_prepare")
@@ -1361,3 +1377,175 @@ def flash_attention_rotating(out: torch.Tensor, qkv: torch.Tensor, k_pages: torc
 
 def flash_scratch_elems(T: int, nh: int, hd: int, splits: int) -> int:
     return 0 if splits <= 1 else T * nh * splits * (hd + 2)
+
+
+# ------------------------------------------------------------------ embedding with a table of token pairs, stream steps
+
+def pair_embedding(out: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor,
+                   positions: torch.Tensor, seq_of_token: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
+                   prev_state: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0,
+                   write_state: bool = True) -> None:
+    """out[t] = table[id] * scale + pairs[(previous id * mul_prev + id * mul_cur) mod buckets] in float32; a request's
+    first token takes pairs[buckets].  prev_state [slots] int32 carries a request's last id from step to step."""
+    _cuda(out, table, pairs, ids, positions, seq_of_token, cu_q, state_slots, prev_state)
+    T, H = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous() and pairs.is_contiguous()
+    assert table.dtype == pairs.dtype and table.shape[1] == H and tuple(pairs.shape) == (buckets + 1, H)
+    assert prev_state.dtype == torch.int32 and prev_state.is_contiguous() and ids.dtype == torch.int32
+    _check(lib().atom_pair_embedding(out.data_ptr(), table.data_ptr(), pairs.data_ptr(), dtype_code(table.dtype),
+                                     ids.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(), cu_q.data_ptr(),
+                                     state_slots.data_ptr(), prev_state.data_ptr(), T, H, table.shape[0], int(buckets),
+                                     int(mul_prev), int(mul_cur), float(scale), int(write_state), _stream()),
+           "pair_embedding")
+
+
+def add_row(residual: torch.Tensor, vec: torch.Tensor) -> None:
+    """residual[t] += vec for every row (float32 sums)."""
+    _cuda(residual, vec)
+    T, H = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and vec.is_contiguous() and vec.numel() == H
+    _check(lib().atom_add_row(residual.data_ptr(), vec.data_ptr(), dtype_code(vec.dtype), T, H, _stream()), "add_row")
+
+
+def normed_add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor, delta_weight: torch.Tensor,
+                       delta_eps: float, weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                       n_rows: Optional[int] = None) -> None:
+    """residual += rmsnorm(delta; delta_weight); out = rmsnorm(residual; weight), one kernel, 32-bit.  With ``rows``
+    only those rows, written densely, and residual is left as it is."""
+    _cuda(out, residual, delta, delta_weight, weight, rows)
+    H = residual.shape[-1]
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
+    assert delta.dtype == out.dtype and delta.is_contiguous() and delta.shape[-1] == H
+    assert weight.numel() == H and delta_weight.numel() == H and weight.dtype == delta_weight.dtype
+    n = (rows.numel() if n_rows is None else n_rows) if rows is not None else residual.shape[0]
+    _check(lib().atom_normed_add_rmsnorm(out.data_ptr(), dtype_code(out.dtype), residual.data_ptr(), delta.data_ptr(),
+                                         delta_weight.data_ptr(), float(delta_eps), weight.data_ptr(),
+                                         dtype_code(weight.dtype), float(eps), _ptr(rows), n, H, _stream()),
+           "normed_add_rmsnorm")
+
+
+def head_gate(x: torch.Tensor, g: torch.Tensor) -> None:
+    """x[t, h, :] *= sigmoid(g[t, h]); x [T, H, n] dense, g [T, H] a view whose rows may lie further apart."""
+    _cuda(x, g)
+    T, H, n = x.shape
+    assert x.is_contiguous() and g.shape == (T, H) and g.stride(1) == 1 and g.dtype == x.dtype
+    _check(lib().atom_head_gate(x.data_ptr(), g.data_ptr(), dtype_code(x.dtype), g.stride(0), T, H, n, _stream()),
+           "head_gate")
+
+
+# ------------------------------------------------------------------ gated linear attention
+
+def gla_supports(dk: int, dv: int) -> bool:
+    return bool(lib().atom_gla_supports(dk, dv))
+
+
+GLA_RUN = 64        # rows per run of the scan in steps of more rows than this
+
+
+def gla_run(T: int) -> int:
+    """Rows per run for a step of T rows (0: every request is walked once)."""
+    if T <= GLA_RUN:
+        return 0
+    return GLA_RUN if T <= 64 * GLA_RUN else -(-T // 64)
+
+
+def gla_scratch_elems(T: int, num_seqs: int, H: int, dk: int, dv: int):
+    """(floats of the runs' sums, floats of the runs' decay products)."""
+    run = gla_run(T)
+    if run == 0:
+        return 0, 0
+    slots = -(-T // run) + num_seqs
+    return slots * H * dk * dv, slots * H * dk
+
+
+def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor,
+             tau: float, q_scale: float, state: torch.Tensor, scratch_b: Optional[torch.Tensor],
+             scratch_a: Optional[torch.Tensor], cu_q: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, H: int,
+             dk: int, dv: int, write_state: bool = True) -> None:
+    """out[t] (float32 [T, H dv]) = S_t^T (q_t q_scale), S_t = diag(a_t) S_(t-1) + k_t v_t^T per head with
+    a_t = sigmoid(z_t + z_bias)^(1 / tau), over every request's rows.  q, k [T, H dk] and v [T, H dv] are views of one
+    array of rows (equal row stride); z [T, H dk] float32; state [slots, H, dk, dv] float32."""
+    _cuda(out, q, k, v, z, z_bias, state, scratch_a, scratch_b, cu_q, state_slots)
+    T = q.shape[0]
+    run = gla_run(T)
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, H * dv)
+    assert q.stride(0) == k.stride(0) == v.stride(0) and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert q.dtype == k.dtype == v.dtype and q.shape[1] == k.shape[1] == H * dk and v.shape[1] == H * dv
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape == (T, H * dk) and z_bias.numel() == H * dk
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv)
+    if run:
+        nb, na = gla_scratch_elems(T, num_seqs, H, dk, dv)
+        assert scratch_b is not None and scratch_a is not None and scratch_b.dtype == scratch_a.dtype == torch.float32
+        assert scratch_b.numel() >= nb and scratch_a.numel() >= na
+    _check(lib().atom_gla_scan(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), dtype_code(q.dtype), q.stride(0),
+                               z.data_ptr(), z.stride(0), z_bias.data_ptr(), dtype_code(z_bias.dtype), float(tau),
+                               float(q_scale), state.data_ptr(), _ptr(scratch_b) if run else None,
+                               _ptr(scratch_a) if run else None, cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, T, H,
+                               dk, dv, run, int(write_state), _stream()), "gla_scan")
+    if run:
+        add_launches(2)      # (the runs' sums, the prefix over the runs, the outputs)
+
+
+def gla_gate_norm(y: torch.Tensor, o: torch.Tensor, g: torch.Tensor, w: torch.Tensor, eps: float, H: int, dv: int,
+                  seq_of_token: torch.Tensor) -> None:
+    """y[t, h] = o[t, h] / rms(o[t, h]) * w * silu(g[t, h]): the norm runs over one head's columns, w [dv] is shared by
+    the heads.  o float32 [T, H dv]; g a view whose rows may lie further apart."""
+    _cuda(y, o, g, w, seq_of_token)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and y.is_contiguous() and y.shape == o.shape == (T, H * dv)
+    assert g.dtype == y.dtype and g.stride(1) == 1 and g.shape == (T, H * dv) and w.numel() == dv
+    _check(lib().atom_gla_gate_norm(y.data_ptr(), o.data_ptr(), g.data_ptr(), dtype_code(y.dtype), g.stride(0),
+                                    w.data_ptr(), dtype_code(w.dtype), T, H, dv, float(eps), seq_of_token.data_ptr(),
+                                    _stream()), "gla_gate_norm")
+
+
+# ------------------------------------------------------------------ attention over a window and pooled blocks
+
+def pooled_attention_supports(H: int, G: int, dk: int, dv: int) -> bool:
+    return bool(lib().atom_pooled_attention_supports(H, G, dk, dv))
+
+
+def pool_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor, pv_pages: torch.Tensor,
+                block_table: torch.Tensor, pool_table: torch.Tensor, page_size: int, positions: torch.Tensor,
+                seq_of_token: torch.Tensor, T: int, pool: int, status: torch.Tensor) -> None:
+    """For every token of the step that ends a block of ``pool`` positions: the means of the block's cached keys and
+    values go to the block's row of the pooled pages.  Pages [pages, kv heads, page, size]."""
+    _cuda(k_pages, v_pages, pk_pages, pv_pages, block_table, pool_table, positions, seq_of_token, status)
+    G, dk, dv = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and pk_pages.is_contiguous() and pv_pages.is_contiguous()
+    assert k_pages.dtype == v_pages.dtype == pk_pages.dtype == pv_pages.dtype
+    assert tuple(pk_pages.shape[1:]) == (G, page_size, dk) and tuple(pv_pages.shape[1:]) == (G, page_size, dv)
+    assert block_table.dtype == pool_table.dtype == torch.int32 and block_table.is_contiguous() and pool_table.is_contiguous()
+    _check(lib().atom_pool_blocks(k_pages.data_ptr(), v_pages.data_ptr(), pk_pages.data_ptr(), pv_pages.data_ptr(),
+                                  dtype_code(k_pages.dtype), block_table.data_ptr(), block_table.shape[1],
+                                  pool_table.data_ptr(), pool_table.shape[1], page_size, k_pages.shape[0],
+                                  pk_pages.shape[0], positions.data_ptr(), seq_of_token.data_ptr(), T, G, dk, dv,
+                                  int(pool), status.data_ptr(), _stream()), "pool_blocks")
+
+
+def pooled_attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     pk_pages: Optional[torch.Tensor], pv_pages: Optional[torch.Tensor], block_table: torch.Tensor,
+                     pool_table: Optional[torch.Tensor], page_size: int, positions: torch.Tensor,
+                     seq_of_token: torch.Tensor, H: int, scale: float, window: int, pool: int, sink: bool,
+                     mix: Optional[torch.Tensor], gate: Optional[torch.Tensor]) -> None:
+    """out[t, h] = sum_x w_h[x] v[x] over the tokens of the window and the pooled blocks before it (see
+    csrc/pooled_attention.cu), times sigmoid(gate[t, h]) with a gate.  q [T, H dk] (rows may lie apart), out [T, H dv]
+    dense, mix [H, H] float32 or None, gate [T, H dv] (rows may lie apart) or None."""
+    _cuda(out, q, k_pages, v_pages, pk_pages, pv_pages, block_table, pool_table, positions, seq_of_token, mix, gate)
+    T = q.shape[0]
+    G, dk, dv = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
+    assert out.is_contiguous() and out.shape == (T, H * dv) and q.shape[1] == H * dk and q.stride(1) == 1
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert mix is None or (mix.dtype == torch.float32 and mix.is_contiguous() and tuple(mix.shape) == (H, H))
+    assert gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1)
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    if pool and window:
+        assert pk_pages is not None and pv_pages is not None and pool_table is not None and pool_table.is_contiguous()
+        assert pk_pages.dtype == pv_pages.dtype == out.dtype and pk_pages.is_contiguous() and pv_pages.is_contiguous()
+    _check(lib().atom_pooled_attention(out.data_ptr(), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+                                       _ptr(pk_pages), _ptr(pv_pages), dtype_code(out.dtype), block_table.data_ptr(),
+                                       block_table.shape[1], _ptr(pool_table),
+                                       pool_table.shape[1] if pool_table is not None else 0, page_size,
+                                       positions.data_ptr(), seq_of_token.data_ptr(), T, H, G, dk, dv, float(scale),
+                                       int(window), int(pool), int(bool(sink)), _ptr(mix), _ptr(gate),
+                                       gate.stride(0) if gate is not None else 0, _stream()), "pooled_attention")

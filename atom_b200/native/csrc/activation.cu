@@ -180,3 +180,34 @@ ATOM_EXPORT int atom_relu2(void* x, int dtype, int64_t n, cudaStream_t stream) {
     return ATOM_ERR_ARG;
   return atom::check_launch();
 }
+
+// x[t, h, :] *= sigmoid(g[t, h]): one gate number per head.  x [T, H, n] dense; g rows ldg apart.
+namespace atom {
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int64_t ldg, int H, int n, int64_t total) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t th = e / n;
+    const int64_t t = th / H;
+    const int h = (int)(th - t * H);
+    const float z = to_float(g[t * ldg + h]);
+    x[e] = from_float<T>(to_float(x[e]) / (1.f + expf(-z)));
+  }
+}
+}  // namespace atom
+
+ATOM_EXPORT int atom_head_gate(void* x, const void* g, int dtype, int64_t ldg, int T, int H, int n, cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (H <= 0 || n <= 0) return ATOM_ERR_ARG;
+  const int64_t total = (int64_t)T * H * n;
+  const int blocks = (int)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)g, ldg, H, n, total);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x,
+                     (const __nv_bfloat16*)g, ldg, H, n, total);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}

@@ -41,15 +41,17 @@ __global__ void latent_prepare_kernel(T* __restrict__ cq, const T* __restrict__ 
   const int s = seq_of_token[t];
   if (s < 0) return;
   const T* row = proj + (int64_t)t * ld;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < Rq; i += blockDim.x) {
-    const float v = to_float(row[q_off + i]);
-    ss = fmaf(v, v, ss);
+  if (Rq > 0) {       // (0: the queries pass no latent of their own)
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < Rq; i += blockDim.x) {
+      const float v = to_float(row[q_off + i]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rq = rsqrtf(ss / (float)Rq + eps);
+    for (int i = threadIdx.x; i < Rq; i += blockDim.x)
+      cq[(int64_t)t * Rq + i] = from_float<T>(to_float(row[q_off + i]) * rq * load_as_float(wq, w_dtype, i));
   }
-  ss = block_sum(ss, scratch);
-  const float rq = rsqrtf(ss / (float)Rq + eps);
-  for (int i = threadIdx.x; i < Rq; i += blockDim.x)
-    cq[(int64_t)t * Rq + i] = from_float<T>(to_float(row[q_off + i]) * rq * load_as_float(wq, w_dtype, i));
   if (pages == nullptr) return;
   const int pos = positions[t];
   const int page = block_table[(int64_t)s * table_width + pos / page_size];
@@ -320,7 +322,7 @@ ATOM_EXPORT int atom_latent_prepare(void* cq, const void* proj, int dtype, int64
                                     const int* seq_of_token, const int* block_table, int table_width, int page_size,
                                     void* pages, int64_t num_pages, int* status, int T, cudaStream_t stream) {
   if (T <= 0) return ATOM_OK;
-  if (Rq <= 0 || dims < 0 || dims % 2 || (pages && (R <= 0 || rd < dims || page_size <= 0))) return ATOM_ERR_ARG;
+  if (Rq < 0 || (Rq > 0 && (!cq || !wq)) || dims < 0 || dims % 2 || (dims > 0 && !freq) || (pages && (R <= 0 || rd < dims || page_size <= 0))) return ATOM_ERR_ARG;
   if (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16) return ATOM_ERR_ARG;
   const int threads = 128;
   if (dtype == ATOM_F32)

@@ -246,3 +246,66 @@ ATOM_EXPORT int atom_rmsnorm(void* out, const void* x, int act_dtype, const void
   }
   return atom::check_launch();
 }
+
+// A sub-block whose output passes an RMSNorm of its own before it enters the residual stream, fused with the norm
+// that reads the stream next:
+//   r = residual[row] + rmsnorm(delta[row]; wd, eps_d);   residual[row] = r (unless rows are picked);
+//   out = rmsnorm(r; w, eps)
+// all in 32-bit; the row's numbers wait in shared memory between the passes.
+namespace atom {
+
+template <typename TA>
+__global__ void normed_add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ residual,
+                                          const TA* __restrict__ delta, const void* __restrict__ wd, float eps_d,
+                                          const void* __restrict__ w, int w_dtype, float eps,
+                                          const int* __restrict__ rows, int H) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  extern __shared__ float row_s[];
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int64_t src = rows ? rows[r] : r;
+  float* res = residual + src * H;
+  const TA* d = delta + src * H;
+  float sd = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = to_float(d[i]);
+    row_s[i] = v;
+    sd = fmaf(v, v, sd);
+  }
+  sd = block_sum(sd, scratch);
+  const float rd = rsqrtf(sd / (float)H + eps_d);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = res[i] + row_s[i] * rd * load_as_float(wd, w_dtype, i);
+    row_s[i] = v;
+    if (!rows) res[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  TA* o = out + (int64_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    o[i] = from_float<TA>(row_s[i] * rstd * load_as_float(w, w_dtype, i));
+}
+
+}  // namespace atom
+
+// wd and w have one type (w_dtype).
+ATOM_EXPORT int atom_normed_add_rmsnorm(void* out, int act_dtype, float* residual, const void* delta, const void* wd,
+                                        float eps_d, const void* w, int w_dtype, float eps, const int* rows, int n_rows,
+                                        int H, cudaStream_t stream) {
+  if (n_rows <= 0) return ATOM_OK;
+  if (H <= 0 || H > 48 * 256 || !delta || !wd || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
+  const int threads = atom::norm_threads(H);
+  const size_t smem = sizeof(float) * (size_t)H;
+  if (act_dtype == ATOM_F32)
+    atom::launch_pdl(atom::normed_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, (float*)out,
+                     residual, (const float*)delta, wd, eps_d, w, w_dtype, eps, rows, H);
+  else if (act_dtype == ATOM_BF16)
+    atom::launch_pdl(atom::normed_add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream,
+                     (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, wd, eps_d, w, w_dtype, eps, rows, H);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}

@@ -1,6 +1,6 @@
 """Parts a model is put together from; importing the package registers the built-in ones."""
-from . import (attention, block, conv_attention, embedding, latent_attention, lightning, mixed_attention, mlp, moe,
-               norm, recurrent, rglru, rope, side_by_side)  # noqa: F401
+from . import (attention, block, conv_attention, embedding, gla, latent_attention, lightning, mixed_attention, mlp, moe,
+               norm, pooled_attention, recurrent, rglru, rope, side_by_side, token_shifted)  # noqa: F401
 from .base import FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, Workspace
 from .registry import build, lookup, register
 from .spec import CacheNeed, LayerSpec, ModelSpec, ParamSpec, PartSpec, RunEntry

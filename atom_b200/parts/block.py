@@ -18,6 +18,11 @@ by whoever comes next (``delta_scale`` tells the model the factor of what ``run`
 "parallel" has one norm whose output both the mixer and the feed-forward read, and adds both to the residual:
    r += delta;  h = norm(r);  r += mixer(h) + ffn(h)        (a layer may have no feed-forward).
 
+"sandwich" puts a norm before and after each sub-block (the feed-forward and its two norms optional):
+   r += delta;  a = norm1(r);  r += norm1b(mixer(a));  [b = norm2(r);  r += norm2b(ffn(b))]
+A sub-block's output travels to the next norm as a ``NormedDelta``, so that the norm after a sub-block, the add and
+the norm before the next sub-block are one kernel.
+
 Between parts that say they can, an output travels as a product still to run and normalised rows
 as ``ScaledRows`` (parts/linear.py), so that in a step of few rows the norms need no kernel of their
 own; a part that says nothing gets and gives plain tensors.
@@ -25,7 +30,7 @@ own; a part that says nothing gets and gives plain tensors.
 from __future__ import annotations
 
 from .. import native
-from .linear import resolve
+from .linear import NormedDelta, resolve
 from .registry import register
 
 
@@ -81,6 +86,38 @@ class ScaledPreNormBlock:
             return x
         b = _add_norm(self.ffn_norm, residual, x, "norm.ffn", self.ffn, delta_scale=m)
         return _forward(self.ffn, b, step)
+
+
+@register("arrangement", "sandwich")
+class SandwichBlock:
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm", "ffn_norm": "norm", "ffn": "ffn",
+             "ffn_post_norm": "norm"}
+    optional = ("ffn_norm", "ffn", "ffn_post_norm")
+    takes_pending = True      # delta may be a NormedDelta (or a PendingProduct), and run() returns a NormedDelta
+
+    def __init__(self, mixer_norm, mixer, mixer_post_norm, ffn_norm=None, ffn=None, ffn_post_norm=None):
+        if len({ffn is None, ffn_norm is None, ffn_post_norm is None}) != 1:
+            raise ValueError("sandwich: a feed-forward and its two norms come together")
+        for n in (mixer_post_norm, ffn_post_norm):
+            if n is not None and getattr(n, "weight_offset", 0.0):
+                raise ValueError("sandwich: the norms after a sub-block take plain weights")
+        self.mixer_norm, self.mixer, self.mixer_post_norm = mixer_norm, mixer, mixer_post_norm
+        self.ffn_norm, self.ffn, self.ffn_post_norm = ffn_norm, ffn, ffn_post_norm
+
+    @staticmethod
+    def _normed(x, norm, tag):
+        out = norm.rt.workspace.get(tag, tuple(x.shape), x.dtype)
+        return NormedDelta(x, norm.w_weight, norm.eps, out)
+
+    def run(self, residual, delta, step, cache, writes_cache):
+        a = self.mixer_norm.add_norm(residual, delta, "norm.mixer")
+        m = self.mixer.forward(a, step, cache, writes_cache)
+        m = self._normed(m, self.mixer_post_norm, "norm.mixer.post")
+        if self.ffn is None:
+            return m
+        b = self.ffn_norm.add_norm(residual, m, "norm.ffn")
+        f = self.ffn.forward(b, step)
+        return self._normed(f, self.ffn_post_norm, "norm.ffn.post")
 
 
 @register("arrangement", "parallel")

@@ -12,6 +12,10 @@ the weighted sum, so the attention kernel reads one row of kv_rank + rot_dim num
 keys and values of cached tokens are never rebuilt.  Rotation: the first ``rot_dims`` numbers of the rotated parts,
 pair (i, i + rot_dims/2), by the frequencies and the magnitude of the position part (parts/rope.py).
 
+Options: ``q_rank`` None leaves the query latent out (q_h = W_q h directly: the first rows of the stacked product, no
+norm, no W_uq); ``rot_dim`` 0 with ``position`` None leaves the rotated part out; ``gate`` "head" gates a head's
+output with ONE number, sigmoid(W_g h)_h, with W_g of ``heads`` rows.
+
 A layer with ``reads_cache_of_other`` has no W_dkv: the run entry gives it the cache slot of the layer whose rows it
 reads (written earlier in the same step), with maps, queries, window, sink and gate of its own.  ``cache_window``
 is the window the cache has to keep for all its readers (None: every row).
@@ -37,10 +41,16 @@ class LatentAttention(Mixer):
     takes_scaled_rows = True      # x may be ScaledRows: the stacked first product finishes the norm
     defers_output = True          # forward(..., defer=True) may hand the output projection on unrun
 
-    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, q_rank: int,
-                 kv_rank: int, scale: float, norm_eps: float, position: PartSpec, window: Optional[int] = None,
-                 cache_window: Optional[int] = None, sink: bool = False, gate: bool = False,
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int,
+                 q_rank: Optional[int], kv_rank: int, scale: float, norm_eps: float, position: Optional[PartSpec],
+                 window: Optional[int] = None, cache_window: Optional[int] = None, sink: bool = False, gate=False,
                  reads_cache_of_other: bool = False):
+        if gate not in (False, True, "head"):
+            raise ValueError(f"latent_attention: gate is False, True or 'head', got {gate!r}")
+        if position is None:
+            if rot_dim:
+                raise ValueError("latent_attention: a rotated part needs a position encoding")
+            position = PartSpec("none")
         self.hidden_size, self.nh, self.dn, self.rd, self.dv = hidden_size, num_heads, head_dim, rot_dim, value_dim
         self.q_rank, self.R, self.scale, self.norm_eps = q_rank, kv_rank, float(scale), norm_eps
         self.window, self.cache_window = window, cache_window
@@ -55,11 +65,11 @@ class LatentAttention(Mixer):
         self._sink = self._ukT = self._uv = self._freq = None
 
     def _in_rows(self):
-        rows = [self.q_rank]
+        rows = [self.q_rank if self.q_rank is not None else self.nh * (self.dn + self.rd)]
         if not self.borrows:
             rows.append(self.R + self.rd)
         if self.gate:
-            rows.append(self.nh * self.dv)
+            rows.append(self.nh if self.gate == "head" else self.nh * self.dv)
         return tuple(rows)
 
     def params(self) -> Dict[str, ParamSpec]:
@@ -67,12 +77,13 @@ class LatentAttention(Mixer):
         rows = self._in_rows()
         p = {
             "in.weight": ParamSpec((sum(rows), W), rows=rows),
-            "dq.norm": ParamSpec((self.q_rank,), role="vector", init="norm"),
-            "uq.weight": ParamSpec((H * (self.dn + self.rd), self.q_rank)),
             "uk.weight": ParamSpec((H * self.dn, self.R)),
             "uv.weight": ParamSpec((H * self.dv, self.R)),
             "o.weight": ParamSpec((W, H * self.dv)),
         }
+        if self.q_rank is not None:
+            p["dq.norm"] = ParamSpec((self.q_rank,), role="vector", init="norm")
+            p["uq.weight"] = ParamSpec((H * (self.dn + self.rd), self.q_rank))
         if not self.borrows:
             p["dkv.norm"] = ParamSpec((self.R,), role="vector", init="norm")
         if self.sink:
@@ -88,7 +99,7 @@ class LatentAttention(Mixer):
         # W_uk,h^T as the matrix of the folded query's product: [H, kv_rank, dim]
         self._ukT = self.w_uk_weight.view(H, self.dn, self.R).transpose(1, 2).contiguous()
         self._uv = self.w_uv_weight.view(H, self.dv, self.R)
-        self._freq = self.position.frequencies(self.rt)
+        self._freq = self.position.frequencies(self.rt) if self.rd else None
 
     def launch_plan(self, step):
         """(query rows of a tensor-core tile, or 0 for the plain kernel; into how many shares every unit's keys are
@@ -118,20 +129,28 @@ class LatentAttention(Mixer):
         proj = linear(x, self.w_in_weight, None, ws.get("lat.in", (T, sum(rows)), dt))
         bt = step.block_tables[cache.group]
         pages = cache.pages["latent"]
-        cq = ws.get("lat.cq", (T, Rq), dt)
         pos = self.position
+        mag = getattr(pos, "magnitude", 1.0)
+        direct = Rq is None         # the queries are the stacked product's first rows as they are
+        cq = None if direct else ws.get("lat.cq", (T, Rq), dt)
+        wq = None if direct else self.w_dq_norm
         if self.borrows or not writes_cache:
-            native.latent_prepare(cq, proj, 0, self.w_dq_norm, self.norm_eps, step.positions, step.seq_of_token)
+            if not direct:
+                native.latent_prepare(cq, proj, 0, wq, self.norm_eps, step.positions, step.seq_of_token)
         else:
-            native.latent_prepare(cq, proj, 0, self.w_dq_norm, self.norm_eps, step.positions, step.seq_of_token,
-                                  kv_off=Rq, kv_rank=R, rot_dim=rd, rot_dims=pos.rotary_dim, wkv=self.w_dkv_norm,
-                                  freq=self._freq, mag=pos.magnitude, block_table=bt, page_size=cache.page_size,
+            native.latent_prepare(cq, proj, 0, wq, self.norm_eps, step.positions, step.seq_of_token,
+                                  kv_off=rows[0], kv_rank=R, rot_dim=rd, rot_dims=pos.rotary_dim, wkv=self.w_dkv_norm,
+                                  freq=self._freq, mag=mag, block_table=bt, page_size=cache.page_size,
                                   pages=pages, status=step.status)
-        q = linear(cq, self.w_uq_weight, None, ws.get("lat.q", (T, H * (dn + rd)), dt)).view(T, H, dn + rd)
+        if direct:
+            q = proj[:, :rows[0]].view(T, H, dn + rd) if proj.stride(0) == rows[0] else \
+                proj.as_strided((T, H, dn + rd), (proj.stride(0), dn + rd, 1))
+        else:
+            q = linear(cq, self.w_uq_weight, None, ws.get("lat.q", (T, H * (dn + rd)), dt)).view(T, H, dn + rd)
         qf = ws.get("lat.qf", (T, H, R + rd), torch.float32)
         native.gemm_batched(qf[:, :, :R], q[:, :, :dn], self._ukT)
-        native.rotate_pairs(qf, R, q, dn, rd, pos.rotary_dim, self._freq, pos.magnitude, step.positions,
-                            step.seq_of_token)
+        if rd:
+            native.rotate_pairs(qf, R, q, dn, rd, pos.rotary_dim, self._freq, mag, step.positions, step.seq_of_token)
         olat = ws.get("lat.olat", (T, H, R), dt)
         tile_rows, nsplit = self.launch_plan(step)
         scratch = None
@@ -146,7 +165,9 @@ class LatentAttention(Mixer):
         heads = ws.get("lat.heads", (T, H, dv), dt)
         native.gemm_batched(heads, olat, self._uv)
         heads = heads.view(T, H * dv)
-        if self.gate:
+        if self.gate == "head":
+            native.head_gate(heads.view(T, H, dv), proj[:, sum(rows) - H:])
+        elif self.gate:
             g_off = sum(rows) - H * dv
             native.sigmoid_mul(heads, proj[:, g_off:])
         out = ws.get("lat.out", (T, self.hidden_size), dt)

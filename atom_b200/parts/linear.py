@@ -48,9 +48,23 @@ class ScaledRows:
         return self.x.dtype
 
 
+class NormedDelta:
+    """A sub-block's output x that enters the residual stream through an RMSNorm of its own, rmsnorm(x; weight),
+    described but not yet normalised: the norm that reads the stream next does both in one kernel; whoever cannot
+    calls ``run()`` and has the normalised rows."""
+    __slots__ = ("x", "weight", "eps", "out")
+
+    def __init__(self, x, weight, eps, out):
+        self.x, self.weight, self.eps, self.out = x, weight, eps, out
+
+    def run(self) -> torch.Tensor:
+        native.rmsnorm(self.out, self.x, self.weight, self.eps)
+        return self.out
+
+
 def resolve(delta):
-    """The tensor of a part's output, whether it came as one or as a product still to run."""
-    return delta.run() if isinstance(delta, PendingProduct) else delta
+    """The tensor of a part's output, whether it came as one or as work still to run."""
+    return delta.run() if isinstance(delta, (PendingProduct, NormedDelta)) else delta
 
 
 def may_defer(x, weight) -> bool:

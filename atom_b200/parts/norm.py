@@ -16,7 +16,7 @@ import torch
 from .. import native
 from . import linear as _linear
 from .base import Norm
-from .linear import PendingProduct, ScaledRows
+from .linear import NormedDelta, PendingProduct, ScaledRows
 from .registry import register
 from .spec import ParamSpec
 
@@ -43,6 +43,14 @@ class RMSNorm(Norm):
     def add_norm(self, residual, delta, tag, rows=None, n_rows=None, scaled_ok=False, delta_scale=1.0):
         """delta_scale: what is added to the residual is delta_scale * delta (a design whose sub-blocks enter the
         residual stream times a constant); the product's residual epilogue takes the factor too."""
+        if isinstance(delta, NormedDelta):
+            # what is added passes a norm of its own first: both norms and the add in one kernel
+            if delta_scale != 1.0:
+                raise ValueError("a normalised delta enters the residual stream as it is")
+            n = residual.shape[0] if rows is None else (rows.numel() if n_rows is None else n_rows)
+            out = self.rt.workspace.get(tag, (n, self.size), self.rt.dtype)
+            native.normed_add_rmsnorm(out, residual, delta.x, delta.weight, delta.eps, self.w_weight, self.eps, rows, n)
+            return out
         if isinstance(delta, PendingProduct):
             if scaled_ok and rows is None and self._folds(residual, delta):
                 M, ws = residual.shape[0], self.rt.workspace

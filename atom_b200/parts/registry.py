@@ -1,5 +1,5 @@
 """Registries of part classes by kind: mixers, feed-forwards, norms, position encodings,
-embeddings, output heads and layer arrangements.  A new part is one class and one
+embeddings, output heads, layer arrangements and parts that act on the residual stream between layers.  A new part is one class and one
 ``register`` call; specs name parts by these keys."""
 from __future__ import annotations
 
@@ -13,6 +13,7 @@ _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "embedding": {},
     "head": {},
     "arrangement": {},
+    "stream": {},
 }
 
 

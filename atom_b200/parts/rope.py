@@ -88,6 +88,42 @@ class RotaryYarn(PositionEncoding):
         raise NotImplementedError("rope_yarn is applied by mixers that take frequencies (latent_attention)")
 
 
+def wavelength_frequencies(rotary_dim: int, theta: float, factor: float, original: float, low: float, high: float):
+    """Frequencies of the rotary pairs stretched by wavelength (the scaling of Llama 3.1): with f_i = theta^(-2i / d) and
+    wavelength l = 2 pi / f_i, a pair keeps f_i where l < original / high, takes f_i / factor where l > original / low,
+    and between the two blends them with s = (original / l - low) / (high - low): (1 - s) f_i / factor + s f_i.
+    Computed in 64-bit."""
+    import math
+
+    out = []
+    for i in range(rotary_dim // 2):
+        f = theta ** (-2.0 * i / rotary_dim)
+        wave = 2.0 * math.pi / f
+        if wave < original / high:
+            out.append(f)
+        elif wave > original / low:
+            out.append(f / factor)
+        else:
+            s = (original / wave - low) / (high - low)
+            out.append((1.0 - s) * f / factor + s * f)
+    return out
+
+
+@register("position", "rope_wavelength")
+class RotaryWavelength(RotaryYarn):
+    """As ``rope_yarn`` (angles position * frequency computed in the kernel, no table), with the frequencies stretched by
+    wavelength when ``scaling`` is given as {factor, original, low, high}; cos and sin keep their magnitude."""
+    graph_safe = True
+
+    def __init__(self, rotary_dim: int, theta: float, scaling: Optional[dict] = None):
+        super().__init__(rotary_dim, theta, None)
+        if scaling:
+            if float(scaling["high"]) == float(scaling["low"]):
+                raise ValueError("rope_wavelength: 'high' and 'low' must differ")
+            self._f = wavelength_frequencies(rotary_dim, self.theta, float(scaling["factor"]), float(scaling["original"]),
+                                             float(scaling["low"]), float(scaling["high"]))
+
+
 @register("position", "none")
 class NoPosition(PositionEncoding):
     graph_safe = True

@@ -78,6 +78,9 @@ class RunEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    # Row of the model's ``stream_steps`` table that is added to the residual stream right before this entry runs
+    # (None: nothing is added): a design that runs a span of layers several times marks every pass this way.
+    add_step: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -100,6 +103,9 @@ class ModelSpec:
     # Longest request the engine takes when its own max_model_len is not given; None: max_position
     # (for models whose design names no longest sequence, max_position is the engine's own bound).
     default_max_len: Optional[int] = None
+    # A part of category "stream" that holds vectors of the residual's width which run entries add to the stream
+    # (``RunEntry.add_step``); None: the design has none.
+    stream_steps: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -123,6 +129,9 @@ class CacheNeed:
                   held in pages.  Giving ``num_kv_heads`` and ``head_dim`` instead stands for the two
                   entries "k" and "v" of that shape each.
     kind "state": one array of fixed shape per request, held in a slot.
+    A need of pages may also keep ``block_entries``: one row of these arrays for every whole block of ``block``
+    consecutive positions (block b holds positions b * block .. b * block + block - 1; a request of n positions has
+    n // block rows), in pages of a group of their own that a window never gives back.
     Either kind may also name ``states``: arrays of fixed shape per request (``CacheEntry`` with the
     whole shape, in the compute type unless ``dtype`` says otherwise), held in the request's slot and
     all zeros at the request's first token.  A mixer that keeps pages and a recurrent state side by
@@ -138,8 +147,12 @@ class CacheNeed:
     state_dtype: str = "float32"
     entries: Tuple[CacheEntry, ...] = ()
     states: Tuple[CacheEntry, ...] = ()
+    block: int = 0
+    block_entries: Tuple[CacheEntry, ...] = ()
 
     def __post_init__(self):
+        if bool(self.block_entries) != (self.block > 0) or (self.block_entries and self.kind != "pages"):
+            raise ValueError("rows per block need a block length and a need of pages")
         names = [e.name for e in self.states]
         if len(set(names)) != len(names) or any(not e.shape for e in self.states):
             raise ValueError(f"state arrays need distinct names and a shape: {self.states}")
@@ -152,6 +165,9 @@ class CacheNeed:
             names = [e.name for e in self.entries]
             if len(set(names)) != len(names) or any(not e.shape for e in self.entries):
                 raise ValueError(f"cache entries need distinct names and a shape per token: {self.entries}")
+
+    def block_group_key(self) -> Optional[Tuple]:
+        return ("blocks", self.block_entries, self.block) if self.block_entries else None
 
     def group_key(self) -> Tuple:
         if self.kind == "pages":
@@ -180,7 +196,8 @@ class CacheNeed:
             states += [CacheEntry(f"{n}.{e.name}", e.shape, e.dtype) for e in c.states]
         if pages:
             c = pages[0][1]
-            return CacheNeed("pages", window=c.window, keep_first=c.keep_first, entries=c.entries, states=tuple(states))
+            return CacheNeed("pages", window=c.window, keep_first=c.keep_first, entries=c.entries, states=tuple(states),
+                             block=c.block, block_entries=c.block_entries)
         if states:
             return CacheNeed("state", states=tuple(states))
         return None
