@@ -1,7 +1,7 @@
-"""Prefill and decode throughput of the Nurinex, Mugulorn and Simivik designs beside Qwen3 dense at equal sizes.
+"""Prefill and decode throughput of the Nurinex, Mugulorn, Simivik and Kibotar designs beside Qwen3 dense at equal sizes.
 
     python -m atom_b200.benchmarks.designs [--sizes 1024x8,2048x16] [--layers 4] [--prefill 2048]
-                                           [--batch 8] [--context 2048] [--kernels] [--only qwen3,simivik]
+                                           [--batch 8] [--context 2048] [--kernels] [--only qwen3,kibotar]
 
 For each size (width x attention heads; head size 128, four query heads to a kv head, feed-forward three
 times the width, vocabulary 32768) two engines are built with random bfloat16 weights and the same number
@@ -13,7 +13,12 @@ channels in as many blocks as heads behind a convolution of 4 taps; and Simivik,
 a convolution of 4 taps (the same heads, all 128 numbers rotated, scores capped at 30, a window of 1024 that keeps the
 first 64 tokens) with a dense relu-squared feed-forward, lightning attention (the same heads, 128 numbers per key and
 value) with 16 experts of the width's size of which 2 are used beside a shared one (three times the width per token,
-as the dense ones), attention with the dense feed-forward, attention with the experts, and so on.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
+as the dense ones), attention with the dense feed-forward, attention with the experts, and so on; and Kibotar, whose
+layers (norms before and after every sub-block, a token shift before every mixer, dense relu-squared feed-forwards) are
+attention through a latent of width / 4 (the same heads, 128 numbers per key and value, a gate per head), attention
+over a window of 1024 and pooled blocks of 64 (the same heads, all 128 numbers rotated with stretched frequencies, a
+sink, mixed weights, an output gate, biases), which runs twice in a row, and gated linear attention (the same heads,
+128 numbers per key and value, a decay of rank 64), so that as many layers run as the other designs have.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
 one step, and decode steps of ``--batch`` requests whose caches hold ``--context`` tokens (captured graphs,
 as the engine runs them).  With ``--kernels`` the kernels of one prefill step and of one decode step are
 listed with their summed device time (the engine's profiler hook), which is what the per-kernel rooflines
@@ -84,6 +89,23 @@ def simivik_config(width: int, heads: int, layers: int) -> dict:
     kinds = [("attention", att, dense), ("lightning", lin, moe), ("attention", att, dense), ("attention", att, moe)]
     return {"architecture": "Simivik", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
             "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds[i % 4] for i in range(layers))]}
+
+
+def kibotar_config(width: int, heads: int, layers: int) -> dict:
+    dense = {"kind": "dense", "ff": 3 * width}
+    lat = {"type": "latent_attention", "mlp": dense,
+           "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": width // 4, "scale": 128 ** -0.5}}
+    att = {"type": "attention", "mlp": dense,
+           "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                     "rot": {"base": 1000000.0, "dims": 128,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+                     "mask": {"size": 1024, "pool": 64}}}
+    gla = {"type": "gla", "mlp": dense, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 64}}
+    kinds = [lat, att, gla]
+    unique = max(2, layers - 1)          # the second layer runs twice: ``layers`` layer runs in all
+    return {"architecture": "Kibotar", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 127, "mul_cur": 7}},
+            "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [kinds[i % 3] for i in range(unique)]}
 
 
 def _runner(cfg: dict, pages: int, max_len: int, batch: int):
@@ -186,9 +208,10 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--kernels", action="store_true", help="list the kernels of one prefill and one decode step")
-    ap.add_argument("--only", default="qwen3,nurinex,mugulorn,simivik", help="the designs to measure, comma-separated")
+    ap.add_argument("--only", default="qwen3,nurinex,mugulorn,simivik,kibotar", help="the designs to measure, comma-separated")
     args = ap.parse_args(argv)
-    configs = {"qwen3": qwen3_config, "nurinex": nurinex_config, "mugulorn": mugulorn_config, "simivik": simivik_config}
+    configs = {"qwen3": qwen3_config, "nurinex": nurinex_config, "mugulorn": mugulorn_config, "simivik": simivik_config,
+               "kibotar": kibotar_config}
     chosen = [d for d in args.only.split(",") if d]
     if any(d not in configs for d in chosen):
         ap.error(f"--only takes {sorted(configs)}")

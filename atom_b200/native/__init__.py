@@ -165,6 +165,8 @@ def set_option(name: str, value: int) -> None:
         l.atom_flash_set_option(key, int(value))
     for l in _mixtc_libs.values():
         l.atom_mixtc_set_option(key, int(value))
+    for l in _pwtc_libs.values():
+        l.atom_pwtc_set_option(key, int(value))
 
 
 def reset_options() -> None:
@@ -1549,3 +1551,74 @@ def pooled_attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, 
                                        positions.data_ptr(), seq_of_token.data_ptr(), T, H, G, dk, dv, float(scale),
                                        int(window), int(pool), int(bool(sink)), _ptr(mix), _ptr(gate),
                                        gate.stride(0) if gate is not None else 0, _stream()), "pooled_attention")
+
+
+_PWTC_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _f, _i, _i, _i, _vp, _vp, _i64, _vp]
+POOLED_TC = True     # False: the plain kernel also where the tensor-core kernel takes the sizes (measurements, tests)
+_pwtc_libs = {}
+
+
+def pooled_attention_tc_supports(nh: int, nkv: int, dk: int, dv: int, dtype: torch.dtype) -> bool:
+    """Sizes the tensor-core kernel takes: bfloat16, up to 16 heads, key and value sizes in steps of 16, a warp's output
+    tiles within its registers, everything within an SM's shared memory."""
+    if dtype != torch.bfloat16 or nh > 16 or nkv <= 0 or nh % nkv or dk % 16 or dv % 16 or dk <= 0 or dv <= 0:
+        return False
+    group = nh // nkv
+    tpg = -(-(group * (dv // 16)) // 16)
+    if nkv * tpg * 8 > 64:
+        return False
+    smem = 2 * (nh * 16 * (dk + 8) + 2 * 64 * (max(dk, dv) + 8)) + 4 * nh * 16 * 72 + 4 * nh * nh + 4 * 2 * nh * 16 + 4 * 2 * 64
+    return smem <= 226 * 1024
+
+
+def pwtc_lib(nh: int, nkv: int, dk: int, dv: int):
+    key = (nh, nkv, dk, dv)
+    l = _pwtc_libs.get(key)
+    if l is None:
+        with _lock:
+            l = _pwtc_libs.get(key)
+            if l is None:
+                path = build_variant("pooled_attention_tc.cu", {"ATOM_PW_NH": nh, "ATOM_PW_NKV": nkv, "ATOM_PW_DK": dk,
+                                                                "ATOM_PW_DV": dv})
+                l = ctypes.CDLL(path)
+                l.atom_pooled_attention_tc.argtypes = _PWTC_SIG
+                l.atom_pooled_attention_tc.restype = ctypes.c_int
+                l.atom_pwtc_set_option.argtypes = [_i, _i]
+                l.atom_pwtc_set_option.restype = ctypes.c_int
+                got = [ctypes.c_int() for _ in range(4)]
+                l.atom_pwtc_sizes(*[ctypes.byref(g) for g in got])
+                if tuple(g.value for g in got) != key:
+                    raise NativeBuildError(f"{path} was built for other sizes")
+                for k, v in _option_values.items():
+                    l.atom_pwtc_set_option(k, v)
+                _pwtc_libs[key] = l
+    return l
+
+
+def pooled_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                        pk_pages: Optional[torch.Tensor], pv_pages: Optional[torch.Tensor], block_table: torch.Tensor,
+                        pool_table: Optional[torch.Tensor], page_size: int, positions: torch.Tensor, cu_q: torch.Tensor,
+                        num_seqs: int, H: int, scale: float, window: int, pool: int, sink: bool,
+                        mix: Optional[torch.Tensor], gate: Optional[torch.Tensor]) -> None:
+    """``pooled_attention`` on the tensor cores (bfloat16): tiles of 16 consecutive tokens of a request with all heads
+    (cu_q: [num_seqs + 1] first token row of every request).  Sizes as ``pooled_attention_tc_supports`` says."""
+    _cuda(out, q, k_pages, v_pages, pk_pages, pv_pages, block_table, pool_table, positions, cu_q, mix, gate)
+    T = q.shape[0]
+    G, dk, dv = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
+    assert out.is_contiguous() and out.shape == (T, H * dv) and q.shape[1] == H * dk and q.stride(1) == 1
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and cu_q.numel() >= num_seqs + 1
+    assert tuple(k_pages.shape[1:]) == (G, page_size, dk) and tuple(v_pages.shape[1:]) == (G, page_size, dv)
+    assert mix is None or (mix.dtype == torch.float32 and mix.is_contiguous() and tuple(mix.shape) == (H, H))
+    assert gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1)
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    if pool and window:
+        assert pk_pages is not None and pv_pages is not None and pool_table is not None and pool_table.is_contiguous()
+        assert pk_pages.dtype == pv_pages.dtype == out.dtype and pk_pages.is_contiguous() and pv_pages.is_contiguous()
+    tiles = -(-T // 16) + num_seqs
+    _check(pwtc_lib(H, G, dk, dv).atom_pooled_attention_tc(
+        out.data_ptr(), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), _ptr(pk_pages), _ptr(pv_pages),
+        block_table.data_ptr(), block_table.shape[1], _ptr(pool_table),
+        pool_table.shape[1] if pool_table is not None else 0, page_size, positions.data_ptr(), cu_q.data_ptr(), num_seqs,
+        tiles, float(scale), int(window), int(pool), int(bool(sink)), _ptr(mix), _ptr(gate),
+        gate.stride(0) if gate is not None else 0, _stream()), "pooled_attention_tc")

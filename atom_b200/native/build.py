@@ -77,7 +77,7 @@ def build_dir() -> str:
 
 # Sources that are compiled per variant (one library per value of their -D parameters), on
 # first use by a model that needs that variant; everything else goes into the core library.
-VARIANT_SOURCES = {"attention_flash.cu", "attention_mixed_tc.cu", "window_attention_tc.cu"}
+VARIANT_SOURCES = {"attention_flash.cu", "attention_mixed_tc.cu", "window_attention_tc.cu", "pooled_attention_tc.cu"}
 
 
 def sources() -> List[str]:
@@ -232,6 +232,10 @@ PREBUILT_MIXED_HEADS = (
 PREBUILT_WINDOW_HEADS = ({"ATOM_WA_DK": 128, "ATOM_WA_DV": 128}, {"ATOM_WA_DK": 64, "ATOM_WA_DV": 64})
 
 
+# Sizes of the attention over a window and pooled blocks on the tensor cores that the build check compiles ahead of use.
+PREBUILT_POOLED_HEADS = ({"ATOM_PW_NH": 8, "ATOM_PW_NKV": 2, "ATOM_PW_DK": 128, "ATOM_PW_DV": 128},)
+
+
 def build_all(verbose: bool = True) -> str:
     """Compiles the core library and the usual variants (the build check); returns the core's path."""
     core = build(verbose=verbose)
@@ -239,6 +243,7 @@ def build_all(verbose: bool = True) -> str:
         list(ex.map(lambda hd: build_variant("attention_flash.cu", {"ATOM_HD": hd}, verbose), PREBUILT_HEAD_DIMS))
         list(ex.map(lambda d: build_variant("attention_mixed_tc.cu", d, verbose), PREBUILT_MIXED_HEADS))
         list(ex.map(lambda d: build_variant("window_attention_tc.cu", d, verbose), PREBUILT_WINDOW_HEADS))
+        list(ex.map(lambda d: build_variant("pooled_attention_tc.cu", d, verbose), PREBUILT_POOLED_HEADS))
     return core
 
 

@@ -115,9 +115,14 @@ class PooledWindowAttention(Mixer):
                                    step.seq_of_token, T, self.pool, step.status)
         o = ws.get("pwa.o", (T, nh * dv), dt)
         gate = proj[:, sum(rows[:3]):] if self.gate else None
-        native.pooled_attention(o, q, cache.k_pages, cache.v_pages, pk, pv, bt, pool_bt, cache.page_size, step.positions,
-                                step.seq_of_token, nh, self.scale, self.window or 0, self.pool or 0, self.zero_sink,
-                                self._talk, gate)
+        if native.POOLED_TC and native.pooled_attention_tc_supports(nh, nkv, dk, dv, dt):
+            native.pooled_attention_tc(o, q, cache.k_pages, cache.v_pages, pk, pv, bt, pool_bt, cache.page_size,
+                                       step.positions, step.cu_q, step.num_seqs, nh, self.scale, self.window or 0,
+                                       self.pool or 0, self.zero_sink, self._talk, gate)
+        else:
+            native.pooled_attention(o, q, cache.k_pages, cache.v_pages, pk, pv, bt, pool_bt, cache.page_size,
+                                    step.positions, step.seq_of_token, nh, self.scale, self.window or 0, self.pool or 0,
+                                    self.zero_sink, self._talk, gate)
         out = ws.get("pwa.out", (T, self.hidden_size), dt)
         bias = self.w_o_bias if self.bias else None
         if defer and bias is None and may_defer(o, self.w_o_weight):

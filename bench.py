@@ -26,7 +26,7 @@ Every weight matrix of the model (tens of GB) is read in every step, far more th
 126 MB L2 holds, so consecutive timed steps do not find their inputs in L2.
 
 ``--designs`` leaves all of the above aside and prints the JSON line of ``atom_b200.benchmarks.designs``:
-prefill and decode throughput of the Nurinex, Mugulorn and Simivik designs beside Qwen3 dense at equal layer sizes
+prefill and decode throughput of the Nurinex, Mugulorn, Simivik and Kibotar designs beside Qwen3 dense at equal layer sizes
 (``--designs 1024x8,2048x16``: width x attention heads; ``--designs-kernels`` adds every kernel's time;
 ``--designs-only qwen3,mugulorn`` measures some of the designs).
 """
@@ -184,7 +184,7 @@ def main() -> int:
     ap.add_argument("--designs", nargs="?", const="1024x8,2048x16", default=None, metavar="SIZES",
                     help="instead of the default workload: Nurinex and Mugulorn beside Qwen3 dense at these sizes "
                          "(width x heads, ...)")
-    ap.add_argument("--designs-only", default=None, metavar="NAMES", help="with --designs: only these designs (qwen3,nurinex,mugulorn,simivik)")
+    ap.add_argument("--designs-only", default=None, metavar="NAMES", help="with --designs: only these designs (qwen3,nurinex,mugulorn,simivik,kibotar)")
     ap.add_argument("--designs-kernels", action="store_true", help="with --designs: list every kernel's device time")
     args = ap.parse_args()
 

@@ -343,9 +343,16 @@ def _plain_attention(x, P, m, zero_sink=True, gate=True):
     return (y - P["o.b"]) * 2.0 + P["o.b"] if not gate else y        # (sigmoid(0) = 1/2)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain"])
 @pytest.mark.parametrize("case", ATT_CASES)
-def test_attention_part_under_every_cut(case, dtype):
+def test_attention_part_under_every_cut(case, dtype, monkeypatch):
+    """(bfloat16 runs the tensor-core kernel where it takes the sizes; "bfloat16-plain" the plain kernel there too.)"""
+    from atom_b200 import native
+    if dtype.endswith("-plain"):
+        if not native.pooled_attention_tc_supports(case[0], case[1], case[2], case[3], torch.bfloat16):
+            pytest.skip("these sizes run the plain kernel anyway")
+        monkeypatch.setattr(native, "POOLED_TC", False)
+        dtype = "bfloat16"
     part, m, P, W = _attention_part(case, dtype)
     page, lens = case[6], dict(zip("abc", case[7]))
     g = torch.Generator().manual_seed(sum(case[7]))
@@ -382,7 +389,13 @@ def _pages(n_rows, G, page, d, dtype, seed, extra=3):
     return table, torch.full((n_pages + extra, G, page, d), float("nan"), dtype=_dt(dtype), device=DEV)
 
 
-def _run_pooled_attention(q, k, v, scale, window, pool, dtype, page, cuts, sink=True, mix=None):
+def _kernels(H, G, dk, dv, dtype):
+    """The kernels that take these sizes: the plain one always, the tensor-core one where it does."""
+    from atom_b200 import native
+    return ["plain", "tc"] if native.pooled_attention_tc_supports(H, G, dk, dv, _dt(dtype)) else ["plain"]
+
+
+def _run_pooled_attention(q, k, v, scale, window, pool, dtype, page, cuts, sink=True, mix=None, kernel="plain"):
     """q [T, H, dk], k [T, G, dk], v [T, G, dv] of ONE request, keys and values laid into scrambled pages and the
     blocks' means formed by the pooling kernel as the tokens come; the queries are run in portions ``cuts``."""
     from atom_b200 import native
@@ -411,8 +424,13 @@ def _run_pooled_attention(q, k, v, scale, window, pool, dtype, page, cuts, sink=
             native.pool_blocks(kp, vp, pkp, pvp, table, ptable, page, pos, seq, n, pool, status)
         o = torch.zeros(n, H * dv, dtype=dt, device=DEV)
         qd = q[at:at + n].reshape(n, H * dk).to(dt).to(DEV).contiguous()
-        native.pooled_attention(o, qd, kp, vp, pkp if pool else None, pvp if pool else None, table,
-                                ptable if pool else None, page, pos, seq, H, scale, window, pool, sink, mixd, None)
+        if kernel == "tc":
+            native.pooled_attention_tc(o, qd, kp, vp, pkp if pool else None, pvp if pool else None, table,
+                                       ptable if pool else None, page, pos, _i32([0, n]), 1, H, scale, window, pool, sink,
+                                       mixd, None)
+        else:
+            native.pooled_attention(o, qd, kp, vp, pkp if pool else None, pvp if pool else None, table,
+                                    ptable if pool else None, page, pos, seq, H, scale, window, pool, sink, mixd, None)
         out[at:at + n] = o
         at += n
     assert at == T and int(status.item()) == 0
@@ -471,8 +489,9 @@ def test_single_keys_at_the_windows_edge_and_in_pooled_blocks(window, pool, dtyp
     if window <= 64:
         cut_sets.append([needle + 1] + [1] * (first - needle + 3) + [T])
     for cuts in cut_sets:
-        got = _run_pooled_attention(q, k, v, 1.0, window, pool, dtype, page, cuts)
-        what = f"window {window}, pool {pool}, cuts {cuts[:4]}"
+      for kernel in _kernels(H, G, dk, dv, dtype):
+        got = _run_pooled_attention(q, k, v, 1.0, window, pool, dtype, page, cuts, kernel=kernel)
+        what = f"{kernel}, window {window}, pool {pool}, cuts {cuts[:4]}"
         for i in range(T):
             if as_token(i) or as_block(i):
                 assert float(got[i, :, 0].min()) > 0.05 / pool, f"{what}: key {needle} is lost at {i}"
@@ -485,7 +504,7 @@ def test_single_keys_at_the_windows_edge_and_in_pooled_blocks(window, pool, dtyp
 def test_sink_of_score_zero_and_weights_mixed_after_the_softmax(dtype):
     """Two keys whose scores are 0 and s: with the sink the second one's weight is e^s / (2 + e^s), without it
     e^s / (1 + e^s); mixing adds other heads' weights, not their scores, and leaves the sink's share alone."""
-    H, G, dk, dv = 3, 1, 16, 8
+    H, G, dk, dv = 3, 1, 16, 16
     k = torch.zeros(2, G, dk, dtype=F64)
     k[1, 0, 0] = 1.0
     v = torch.zeros(2, G, dv, dtype=F64)
@@ -494,16 +513,17 @@ def test_sink_of_score_zero_and_weights_mixed_after_the_softmax(dtype):
     s = torch.tensor([0.5, 4.0, -3.0], dtype=F64)
     q[1, :, 0] = s
     e = torch.exp(s)
-    for sink in (True, False):
-        p = e / ((2.0 if sink else 1.0) + e)
-        got = _run_pooled_attention(q, k, v, 1.0, 0, 0, dtype, 8, [2], sink=sink)
-        _close(got[1, :, 0], p, dtype, f"sink {sink}", scale=1.0, f32=1e-6, bf16=4e-3)
-        mix = torch.tensor([[1.0, 0.5, 0.0], [0.0, -1.0, 2.0], [0.25, 0.25, 0.25]], dtype=F64)
-        got = _run_pooled_attention(q, k, v, 1.0, 0, 0, dtype, 8, [2], sink=sink, mix=mix)
-        _close(got[1, :, 0], mix @ p, dtype, f"mixed, sink {sink}", scale=1.0, f32=1e-6, bf16=4e-3)
-    # the first token sees itself and the sink only
-    got = _run_pooled_attention(q, k, v, 1.0, 5, 2, dtype, 8, [1, 1])
-    assert float(got[0].abs().max()) == 0.0
+    for kernel in _kernels(H, G, dk, dv, dtype):
+        for sink in (True, False):
+            p = e / ((2.0 if sink else 1.0) + e)
+            got = _run_pooled_attention(q, k, v, 1.0, 0, 0, dtype, 8, [2], sink=sink, kernel=kernel)
+            _close(got[1, :, 0], p, dtype, f"{kernel}, sink {sink}", scale=1.0, f32=1e-6, bf16=4e-3)
+            mix = torch.tensor([[1.0, 0.5, 0.0], [0.0, -1.0, 2.0], [0.25, 0.25, 0.25]], dtype=F64)
+            got = _run_pooled_attention(q, k, v, 1.0, 0, 0, dtype, 8, [2], sink=sink, mix=mix, kernel=kernel)
+            _close(got[1, :, 0], mix @ p, dtype, f"{kernel}, mixed, sink {sink}", scale=1.0, f32=1e-6, bf16=4e-3)
+        # the first token sees itself and the sink only
+        got = _run_pooled_attention(q, k, v, 1.0, 5, 2, dtype, 8, [1, 1], kernel=kernel)
+        assert float(got[0].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -522,9 +542,36 @@ def test_far_block_among_hundreds(dtype):
     q, k, v = _rounded(q, dtype), _rounded(k, dtype), _rounded(v, dtype)
     want = _plain_weights(q, k, v, 1.0, window, pool)
     for cuts in ([T], [T - 40] + [1] * 40, [700, 3, 900, T]):
-        got = _run_pooled_attention(q, k, v, 1.0, window, pool, dtype, page, cuts)
-        assert float(got[-1, :, 0].min()) > 0.05 / pool
-        _close(got[-60:], want[-60:], dtype, f"cuts {cuts[:3]}", f32=2e-5, bf16=1e-2)
+        for kernel in _kernels(H, G, dk, dv, dtype):
+            got = _run_pooled_attention(q, k, v, 1.0, window, pool, dtype, page, cuts, kernel=kernel)
+            assert float(got[-1, :, 0].min()) > 0.5 / pool
+            _close(got[-60:], want[-60:], dtype, f"{kernel}, cuts {cuts[:3]}", f32=2e-5, bf16=1e-2)
+
+
+TC_CASES = [  # H, G, dk, dv, window, pool, page, T, talk
+    (4, 2, 16, 32, 24, 4, 16, 200, True), (8, 2, 64, 64, 136, 16, 16, 333, True), (6, 3, 80, 48, 90, 7, 16, 300, True),
+    (4, 1, 128, 128, 0, 0, 16, 270, False), (2, 2, 256, 16, 65, 64, 8, 200, True), (3, 1, 48, 112, 1, 1, 16, 150, True),
+    (5, 5, 32, 80, 200, 0, 64, 520, False), (16, 4, 128, 128, 100, 32, 16, 600, True), (16, 8, 32, 32, 17, 16, 16, 210, True),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tensor_core_attention_against_plain_weights(case):
+    """The tensor-core kernel on sharp random scores: prompts of several tiles, portions that start in the middle of a
+    tile of keys or of a block, and single tokens."""
+    from atom_b200 import native
+    H, G, dk, dv, window, pool, page, T, talk = case
+    assert native.pooled_attention_tc_supports(H, G, dk, dv, torch.bfloat16)
+    g = torch.Generator().manual_seed(T + dk)
+    q = _rounded(torch.randn(T, H, dk, generator=g), "bfloat16")
+    k = _rounded(torch.randn(T, G, dk, generator=g), "bfloat16")
+    v = _rounded(torch.randn(T, G, dv, generator=g), "bfloat16")
+    mix = _rounded(torch.eye(H) * 0.7 + torch.randn(H, H, generator=g) * 0.3, "bfloat16") if talk else None
+    scale = 3.0 / dk ** 0.5
+    want = _plain_weights(q, k, v, scale, window, pool, mix=mix)
+    for cuts in ([T], [T - 9] + [1] * 9, [13, 64, 5, 2, 129, 2, 70, 3, 17] * 8):
+        got = _run_pooled_attention(q, k, v, scale, window, pool, "bfloat16", page, cuts, mix=mix, kernel="tc")
+        _close(got, want, "bfloat16", f"cuts {cuts[:3]}", bf16=1e-2)
 
 
 # ============================================================================= whole models
