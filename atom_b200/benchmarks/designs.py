@@ -122,13 +122,28 @@ def _short(name: str) -> str:
     return re.sub(r"\(.*", "", name).replace("atom::", "").replace("void ", "")[:60]
 
 
-def _kernels(fn) -> Dict[str, float]:
-    """Kernel name -> summed device time (us) over one call of fn."""
+def _kernels(fn, runner=None) -> Dict[str, float]:
+    """Kernel name -> summed device time (us) over one call of fn.  With ``runner`` the call runs eagerly and with
+    plain launches: under dependent launch a kernel's time holds its wait for the kernel before it, and a captured
+    graph keeps the launches it was recorded with."""
     from torch.profiler import ProfilerActivity, profile
 
-    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
-        fn()
+    from atom_b200 import native
+
+    graphs = None
+    if runner is not None:
+        graphs, runner.graphs_enabled = runner.graphs_enabled, False
+        native.set_option("pdl", 0)
+        fn()                              # (buffers of the eager path are made outside the listing)
         torch.cuda.synchronize()
+    try:
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            fn()
+            torch.cuda.synchronize()
+    finally:
+        if runner is not None:
+            runner.graphs_enabled = graphs
+            native.set_option("pdl", 1)
     out: Dict[str, float] = {}
     for e in prof.events():
         if e.device_type is not None and str(e.device_type).endswith("CUDA") and e.device_time > 0 and not e.name.startswith("Memcpy"):
@@ -165,8 +180,10 @@ def measure(cfg: dict, n_prefill: int, batch: int, context: int, kernels: bool) 
     out = {"prefill_ms": round(statistics.median(times), 3),
            "prefill_tokens_per_s": round(n_prefill / (statistics.median(times) * 1e-3), 1)}
     if kernels:
-        out["prefill_kernels_us"] = {k: round(v, 1) for k, v in _kernels(prefill_once).items()}
-        runner.finish("p")
+        def prefill_and_finish():
+            prefill_once()
+            runner.finish("p")
+        out["prefill_kernels_us"] = {k: round(v, 1) for k, v in _kernels(prefill_and_finish, runner).items()}
 
     ids = [f"d{i}" for i in range(batch)]
     start = context - 24
@@ -192,7 +209,7 @@ def measure(cfg: dict, n_prefill: int, batch: int, context: int, kernels: bool) 
     out.update(decode_ms_per_step=round(ms, 4), decode_tokens_per_s=round(batch / (ms * 1e-3), 1),
                decode_graph=bool(runner.graph_replays))
     if kernels:
-        out["decode_kernels_us"] = {k: round(v, 1) for k, v in _kernels(decode_once).items()}
+        out["decode_kernels_us"] = {k: round(v, 1) for k, v in _kernels(decode_once, runner).items()}
     runner.check_status()
     out["weight_gb"] = round(runner.weight_bytes / 1e9, 3)
     del runner

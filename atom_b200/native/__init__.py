@@ -67,6 +67,9 @@ _SIGNATURES = {
                       _i, _i, _i, _vp],
     "atom_gla_gate_norm": [_vp, _vp, _vp, _i, _i64, _vp, _i, _i, _i, _i, _f, _vp, _vp],
     "atom_pooled_attention_supports": [_i, _i, _i, _i],
+    "atom_pooled_attention_split_supports": [_i, _i, _i, _i],
+    "atom_pooled_attention_split": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i,
+                                    _i, _i, _f, _i, _i, _i, _vp, _vp, _i64, _i, _vp],
     "atom_pool_blocks": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "atom_pooled_attention": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i,
                               _f, _i, _i, _i, _vp, _vp, _i64, _vp],
@@ -1466,7 +1469,8 @@ def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
              dk: int, dv: int, write_state: bool = True) -> None:
     """out[t] (float32 [T, H dv]) = S_t^T (q_t q_scale), S_t = diag(a_t) S_(t-1) + k_t v_t^T per head with
     a_t = sigmoid(z_t + z_bias)^(1 / tau), over every request's rows.  q, k [T, H dk] and v [T, H dv] are views of one
-    array of rows (equal row stride); z [T, H dk] float32; state [slots, H, dk, dv] float32."""
+    array of rows (equal row stride); z [T, H dk] float32 (steps that are cut into runs leave the decays in it);
+    state [slots, H, dk, dv] float32."""
     _cuda(out, q, k, v, z, z_bias, state, scratch_a, scratch_b, cu_q, state_slots)
     T = q.shape[0]
     run = gla_run(T)
@@ -1485,7 +1489,7 @@ def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
                                _ptr(scratch_a) if run else None, cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, T, H,
                                dk, dv, run, int(write_state), _stream()), "gla_scan")
     if run:
-        add_launches(2)      # (the runs' sums, the prefix over the runs, the outputs)
+        add_launches(3)      # (the decays, the runs' sums, the prefix over the runs, the outputs)
 
 
 def gla_gate_norm(y: torch.Tensor, o: torch.Tensor, g: torch.Tensor, w: torch.Tensor, eps: float, H: int, dv: int,
@@ -1551,6 +1555,53 @@ def pooled_attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, 
                                        positions.data_ptr(), seq_of_token.data_ptr(), T, H, G, dk, dv, float(scale),
                                        int(window), int(pool), int(bool(sink)), _ptr(mix), _ptr(gate),
                                        gate.stride(0) if gate is not None else 0, _stream()), "pooled_attention")
+
+
+def pooled_attention_split_supports(H: int, G: int, dk: int, dv: int) -> bool:
+    return bool(lib().atom_pooled_attention_split_supports(H, G, dk, dv))
+
+
+POOLED_SPLIT_ROWS = 64      # steps of up to this many tokens share every token's keys out among CTAs (0: never)
+
+
+def pooled_attention_splits(T: int, longest: int) -> int:
+    """Into how many shares a step of T tokens cuts every token's keys (``longest``: the most keys a token sees): two
+    CTAs per SM fill the device, in shares of at least 64 keys."""
+    return max(1, min(-(-2 * SM_COUNT // max(T, 1)), -(-longest // 64), 64))
+
+
+def pooled_attention_scratch_elems(T: int, H: int, G: int, dv: int, nsplit: int) -> int:
+    return T * nsplit * (2 * H + H * G * dv)
+
+
+def pooled_attention_split(out: torch.Tensor, scratch: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, pk_pages: Optional[torch.Tensor], pv_pages: Optional[torch.Tensor],
+                           block_table: torch.Tensor, pool_table: Optional[torch.Tensor], page_size: int,
+                           positions: torch.Tensor, seq_of_token: torch.Tensor, H: int, scale: float, window: int,
+                           pool: int, sink: bool, mix: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                           nsplit: int) -> None:
+    """``pooled_attention`` for steps of few tokens: every token's keys are shared out among ``nsplit`` CTAs, which
+    leave unnormalised sums per (head, kv head) in ``scratch``; a merge kernel puts them together, divides and mixes
+    the heads (csrc/pooled_attention.cu)."""
+    _cuda(out, scratch, q, k_pages, v_pages, pk_pages, pv_pages, block_table, pool_table, positions, seq_of_token, mix, gate)
+    T = q.shape[0]
+    G, dk, dv = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
+    assert out.is_contiguous() and out.shape == (T, H * dv) and q.shape[1] == H * dk and q.stride(1) == 1
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert mix is None or (mix.dtype == torch.float32 and mix.is_contiguous() and tuple(mix.shape) == (H, H))
+    assert gate is None or (gate.dtype == out.dtype and gate.shape == out.shape and gate.stride(1) == 1)
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert scratch.dtype == torch.float32 and scratch.numel() >= pooled_attention_scratch_elems(T, H, G, dv, nsplit)
+    if pool and window:
+        assert pk_pages is not None and pv_pages is not None and pool_table is not None and pool_table.is_contiguous()
+        assert pk_pages.dtype == pv_pages.dtype == out.dtype and pk_pages.is_contiguous() and pv_pages.is_contiguous()
+    _check(lib().atom_pooled_attention_split(
+        out.data_ptr(), scratch.data_ptr(), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+        _ptr(pk_pages), _ptr(pv_pages), dtype_code(out.dtype), block_table.data_ptr(), block_table.shape[1],
+        _ptr(pool_table), pool_table.shape[1] if pool_table is not None else 0, page_size, positions.data_ptr(),
+        seq_of_token.data_ptr(), T, H, G, dk, dv, float(scale), int(window), int(pool), int(bool(sink)), _ptr(mix),
+        _ptr(gate), gate.stride(0) if gate is not None else 0, int(nsplit), _stream()), "pooled_attention_split")
+    add_launches(1)      # (the merge)
 
 
 _PWTC_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _f, _i, _i, _i, _vp, _vp, _i64, _vp]

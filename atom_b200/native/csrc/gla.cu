@@ -13,7 +13,8 @@
 //           state after the step
 //   mode 2  every run from its S_begin: the outputs
 // and a step of few rows walks each request once (mode 0: slot in, outputs, slot out).  The cut into runs depends on
-// the step's rows alone and changes only the order of 32-bit roundings.
+// the step's rows alone and changes only the order of 32-bit roundings.  In steps that are cut into runs every CTA
+// of both walks would form the same decays again, so a kernel of its own turns z into the decays in place first.
 //
 //   gla_gate_norm_kernel   y = o / rms(o over a head's columns) * w * silu(g), w shared by the heads
 #include "common.cuh"
@@ -99,8 +100,9 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ q, const T* __res
         const int64_t off = (int64_t)(c0 + row) * ld + (int64_t)hd * dk + i;
         qq = to_float(q[off]) * q_scale;
         kk = to_float(k[off]);
-        aa = gla_decay(z[(int64_t)(c0 + row) * ldz + (int64_t)hd * dk + i] + load_as_float(zb, zb_dtype, (int64_t)hd * dk + i),
-                       inv_tau);
+        const float zz = z[(int64_t)(c0 + row) * ldz + (int64_t)hd * dk + i];
+        // (zb null: z holds the decays already)
+        aa = zb ? gla_decay(zz + load_as_float(zb, zb_dtype, (int64_t)hd * dk + i), inv_tau) : zz;
       }
       q_s[e] = qq;
       k_s[e] = kk;
@@ -158,6 +160,19 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ q, const T* __res
   }
 }
 
+// z[t, i] <- sigmoid(z[t, i] + b[i])^(1/tau), in place.
+__global__ void gla_decay_kernel(float* __restrict__ z, int64_t ldz, const void* __restrict__ zb, int zb_dtype,
+                                 float inv_tau, int n, int64_t total) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = e / n;
+    const int i = (int)(e - t * n);
+    float* p = z + t * ldz + i;
+    *p = gla_decay(*p + load_as_float(zb, zb_dtype, i), inv_tau);
+  }
+}
+
 // Per request and state element, over the request's runs in order: sB[run] <- the state the run begins with, and the
 // slot takes the state after the last run.
 __global__ void gla_prefix_kernel(float* __restrict__ state, float* __restrict__ sB, const float* __restrict__ sA,
@@ -210,7 +225,7 @@ __global__ void gla_gate_norm_kernel(T* __restrict__ y, const float* __restrict_
 }
 
 template <typename T, int KPT>
-static int launch_gla(float* out, const T* q, const T* k, const T* v, int64_t ld, const float* z, int64_t ldz,
+static int launch_gla(float* out, const T* q, const T* k, const T* v, int64_t ld, float* z, int64_t ldz,
                       const void* zb, int zb_dtype, float inv_tau, float q_scale, float* state, float* sB, float* sA,
                       const int* cu_q, const int* state_slots, int num_seqs, int T_, int H, int dk, int dv, int run,
                       int write_state, cudaStream_t stream) {
@@ -228,10 +243,16 @@ static int launch_gla(float* out, const T* q, const T* k, const T* v, int64_t ld
     return check_launch();
   }
   const int slots = (T_ + run - 1) / run + num_seqs;
+  {
+    const int64_t total = (int64_t)T_ * H * dk;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    launch_pdl(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, z, ldz, zb, zb_dtype, inv_tau, H * dk, total);
+    zb = nullptr;
+  }
   launch_pdl(gla_scan_kernel<T, KPT, 1>, dim3(slots, H, colb), dim3(kGlaThreads), smem, stream, out, q, k, v, ld, z, ldz,
              zb, zb_dtype, inv_tau, q_scale, state, sB, sA, cu_q, state_slots, num_seqs, H, dk, dv, run, write_state);
   const int eb = (dk * dv + 255) / 256;
-  launch_pdl(gla_prefix_kernel, dim3(num_seqs, H, eb > 8 ? 8 : eb), dim3(256), 0, stream, state, sB, (const float*)sA,
+  launch_pdl(gla_prefix_kernel, dim3(num_seqs, H, eb > 64 ? 64 : eb), dim3(256), 0, stream, state, sB, (const float*)sA,
              cu_q, state_slots, H, dk, dv, run, write_state);
   launch_pdl(gla_scan_kernel<T, KPT, 2>, dim3(slots, H, colb), dim3(kGlaThreads), smem, stream, out, q, k, v, ld, z, ldz,
              zb, zb_dtype, inv_tau, q_scale, state, sB, sA, cu_q, state_slots, num_seqs, H, dk, dv, run, write_state);
@@ -239,7 +260,7 @@ static int launch_gla(float* out, const T* q, const T* k, const T* v, int64_t ld
 }
 
 template <typename T>
-static int dispatch_gla(float* out, const T* q, const T* k, const T* v, int64_t ld, const float* z, int64_t ldz,
+static int dispatch_gla(float* out, const T* q, const T* k, const T* v, int64_t ld, float* z, int64_t ldz,
                         const void* zb, int zb_dtype, float inv_tau, float q_scale, float* state, float* sB, float* sA,
                         const int* cu_q, const int* state_slots, int num_seqs, int T_, int H, int dk, int dv, int run,
                         int write_state, cudaStream_t stream) {
@@ -262,10 +283,10 @@ static int dispatch_gla(float* out, const T* q, const T* k, const T* v, int64_t 
 
 ATOM_EXPORT int atom_gla_supports(int dk, int dv) { return dk > 0 && dk <= 256 && dv > 0 ? 1 : 0; }
 
-// run 0: every request is walked once.  Otherwise sB holds (ceil(T / run) + num_seqs) * H * dk * dv floats and sA
+// run 0: every request is walked once.  Otherwise z is overwritten with the decays, sB holds (ceil(T / run) + num_seqs) * H * dk * dv floats and sA
 // (ceil(T / run) + num_seqs) * H * dk.
 ATOM_EXPORT int atom_gla_scan(float* out, const void* q, const void* k, const void* v, int dtype, int64_t ld,
-                              const float* z, int64_t ldz, const void* zb, int zb_dtype, float tau, float q_scale,
+                              float* z, int64_t ldz, const void* zb, int zb_dtype, float tau, float q_scale,
                               float* state, float* sB, float* sA, const int* cu_q, const int* state_slots, int num_seqs,
                               int T, int H, int dk, int dv, int run, int write_state, cudaStream_t stream) {
   if (T <= 0 || num_seqs <= 0) return ATOM_OK;

@@ -289,6 +289,87 @@ __global__ void normed_add_rmsnorm_kernel(TA* __restrict__ out, float* __restric
     o[i] = from_float<TA>(row_s[i] * rstd * load_as_float(w, w_dtype, i));
 }
 
+// The same for bfloat16 rows of a multiple of 8 numbers, at most 8 * NV * blockDim: a thread keeps its 8 * NV numbers in
+// registers, so that every array is read once and written once, 16 bytes at a time.
+__device__ __forceinline__ void load8(const void* w, int w_dtype, int i, float (&o)[8]) {
+  if (w_dtype == ATOM_F32) {
+    const float4 a = *reinterpret_cast<const float4*>((const float*)w + i);
+    const float4 b = *reinterpret_cast<const float4*>((const float*)w + i + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  } else {
+    const uint4 q = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)w + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      o[2 * e] = f.x;
+      o[2 * e + 1] = f.y;
+    }
+  }
+}
+
+template <int NV>
+__global__ void normed_add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual,
+                                                   const __nv_bfloat16* __restrict__ delta, const void* __restrict__ wd,
+                                                   float eps_d, const void* __restrict__ w, int w_dtype, float eps,
+                                                   const int* __restrict__ rows, int H) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int64_t src = rows ? rows[r] : r;
+  float v[NV][8];
+  float sd = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      load8(delta + src * H, ATOM_BF16, i, v[k]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sd = fmaf(v[k][e], v[k][e], sd);
+    }
+  }
+  sd = block_sum(sd, scratch);
+  const float rd = rsqrtf(sd / (float)H + eps_d);
+  float* res = residual + src * H;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      float wv[8], rv[8];
+      load8(wd, w_dtype, i, wv);
+      load8(res, ATOM_F32, i, rv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[k][e] = rv[e] + v[k][e] * rd * wv[e];
+        ss = fmaf(v[k][e], v[k][e], ss);
+      }
+      if (!rows) {
+        *reinterpret_cast<float4*>(res + i) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+        *reinterpret_cast<float4*>(res + i + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
+      }
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  __nv_bfloat16* o = out + (int64_t)r * H;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      float wv[8];
+      load8(w, w_dtype, i, wv);
+      uint4 q;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        h[e] = __floats2bfloat162_rn(v[k][2 * e] * rstd * wv[2 * e], v[k][2 * e + 1] * rstd * wv[2 * e + 1]);
+      *reinterpret_cast<uint4*>(o + i) = q;
+    }
+  }
+}
+
 }  // namespace atom
 
 // wd and w have one type (w_dtype).
@@ -299,6 +380,24 @@ ATOM_EXPORT int atom_normed_add_rmsnorm(void* out, int act_dtype, float* residua
   if (H <= 0 || H > 48 * 256 || !delta || !wd || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
   const int threads = atom::norm_threads(H);
   const size_t smem = sizeof(float) * (size_t)H;
+  const bool aligned = ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
+                       ((uintptr_t)w % 16 == 0) && ((uintptr_t)wd % 16 == 0);
+  if (act_dtype == ATOM_BF16 && H % 8 == 0 && H <= 8 * 2 * 1024 && aligned) {
+    const int vecs = H / 8;
+    int nv = 1, th = ((vecs + 31) / 32) * 32;
+    if (th > 1024) {
+      nv = 2;
+      th = (((vecs + 1) / 2 + 31) / 32) * 32;
+    }
+    if (th < 64) th = 64;
+    if (nv == 1)
+      atom::launch_pdl(atom::normed_add_rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out,
+                       residual, (const __nv_bfloat16*)delta, wd, eps_d, w, w_dtype, eps, rows, H);
+    else
+      atom::launch_pdl(atom::normed_add_rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out,
+                       residual, (const __nv_bfloat16*)delta, wd, eps_d, w, w_dtype, eps, rows, H);
+    return atom::check_launch();
+  }
   if (act_dtype == ATOM_F32)
     atom::launch_pdl(atom::normed_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, (float*)out,
                      residual, (const float*)delta, wd, eps_d, w, w_dtype, eps, rows, H);

@@ -92,6 +92,26 @@ class PooledWindowAttention(Mixer):
                 b = torch.cat([b, torch.zeros(self.nh * self.dv, dtype=b.dtype, device=b.device)])
             self._in_bias = b.contiguous()
 
+    def launch_plan(self, step):
+        """("split", shares) for steps of few tokens: every token's keys are shared out among CTAs; ("tiles", 0) for the
+        tensor-core kernel's tiles of 16 tokens; ("tokens", 0) for the plain kernel, a CTA a token."""
+        key = ("pooled_window_attention", self.nh, self.nkv, self.dk, self.dv, self.window or 0, self.pool or 0)
+        plan = step.plans.get(key)
+        if plan is None:
+            T = step.num_tokens
+            if native.POOLED_SPLIT_ROWS and T <= native.POOLED_SPLIT_ROWS and \
+                    native.pooled_attention_split_supports(self.nh, self.nkv, self.dk, self.dv):
+                longest = min(step.max_ctx_len, self.window) if self.window else step.max_ctx_len
+                if self.pool:
+                    longest += step.max_ctx_len // self.pool
+                plan = ("split", native.pooled_attention_splits(T, max(longest, 1)))
+            elif native.POOLED_TC and native.pooled_attention_tc_supports(self.nh, self.nkv, self.dk, self.dv, self.rt.dtype):
+                plan = ("tiles", 0)
+            else:
+                plan = ("tokens", 0)
+            step.plans[key] = plan
+        return plan
+
     def forward(self, x, step, cache, writes_cache, defer=False):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
@@ -115,7 +135,13 @@ class PooledWindowAttention(Mixer):
                                    step.seq_of_token, T, self.pool, step.status)
         o = ws.get("pwa.o", (T, nh * dv), dt)
         gate = proj[:, sum(rows[:3]):] if self.gate else None
-        if native.POOLED_TC and native.pooled_attention_tc_supports(nh, nkv, dk, dv, dt):
+        how, nsplit = self.launch_plan(step)
+        if how == "split":
+            scratch = ws.get("pwa.shares", (native.pooled_attention_scratch_elems(T, nh, nkv, dv, nsplit),), torch.float32)
+            native.pooled_attention_split(o, scratch, q, cache.k_pages, cache.v_pages, pk, pv, bt, pool_bt, cache.page_size,
+                                          step.positions, step.seq_of_token, nh, self.scale, self.window or 0,
+                                          self.pool or 0, self.zero_sink, self._talk, gate, nsplit)
+        elif how == "tiles":
             native.pooled_attention_tc(o, q, cache.k_pages, cache.v_pages, pk, pv, bt, pool_bt, cache.page_size,
                                        step.positions, step.cu_q, step.num_seqs, nh, self.scale, self.window or 0,
                                        self.pool or 0, self.zero_sink, self._talk, gate)

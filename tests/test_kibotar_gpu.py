@@ -343,16 +343,20 @@ def _plain_attention(x, P, m, zero_sink=True, gate=True):
     return (y - P["o.b"]) * 2.0 + P["o.b"] if not gate else y        # (sigmoid(0) = 1/2)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain", "float32-whole"])
 @pytest.mark.parametrize("case", ATT_CASES)
 def test_attention_part_under_every_cut(case, dtype, monkeypatch):
-    """(bfloat16 runs the tensor-core kernel where it takes the sizes; "bfloat16-plain" the plain kernel there too.)"""
+    """(bfloat16 runs the tensor-core kernel where it takes the sizes; "bfloat16-plain" the plain kernel there too;
+    steps of few tokens share their keys out among CTAs, "float32-whole" leaves that form out.)"""
     from atom_b200 import native
     if dtype.endswith("-plain"):
         if not native.pooled_attention_tc_supports(case[0], case[1], case[2], case[3], torch.bfloat16):
             pytest.skip("these sizes run the plain kernel anyway")
         monkeypatch.setattr(native, "POOLED_TC", False)
         dtype = "bfloat16"
+    if dtype.endswith("-whole"):
+        monkeypatch.setattr(native, "POOLED_SPLIT_ROWS", 0)
+        dtype = "float32"
     part, m, P, W = _attention_part(case, dtype)
     page, lens = case[6], dict(zip("abc", case[7]))
     g = torch.Generator().manual_seed(sum(case[7]))
@@ -392,7 +396,10 @@ def _pages(n_rows, G, page, d, dtype, seed, extra=3):
 def _kernels(H, G, dk, dv, dtype):
     """The kernels that take these sizes: the plain one always, the tensor-core one where it does."""
     from atom_b200 import native
-    return ["plain", "tc"] if native.pooled_attention_tc_supports(H, G, dk, dv, _dt(dtype)) else ["plain"]
+    out = ["plain"]
+    if native.pooled_attention_split_supports(H, G, dk, dv):
+        out += ["split1", "split3", "split7"]          # the keys of every token alone, and shared out among 3 and 7 CTAs
+    return out + (["tc"] if native.pooled_attention_tc_supports(H, G, dk, dv, _dt(dtype)) else [])
 
 
 def _run_pooled_attention(q, k, v, scale, window, pool, dtype, page, cuts, sink=True, mix=None, kernel="plain"):
@@ -424,7 +431,14 @@ def _run_pooled_attention(q, k, v, scale, window, pool, dtype, page, cuts, sink=
             native.pool_blocks(kp, vp, pkp, pvp, table, ptable, page, pos, seq, n, pool, status)
         o = torch.zeros(n, H * dv, dtype=dt, device=DEV)
         qd = q[at:at + n].reshape(n, H * dk).to(dt).to(DEV).contiguous()
-        if kernel == "tc":
+        if kernel.startswith("split"):
+            ns = int(kernel[5:])
+            scratch = torch.full((native.pooled_attention_scratch_elems(n, H, G, dv, ns),), float("nan"),
+                                 dtype=torch.float32, device=DEV)
+            native.pooled_attention_split(o, scratch, qd, kp, vp, pkp if pool else None, pvp if pool else None, table,
+                                          ptable if pool else None, page, pos, seq, H, scale, window, pool, sink, mixd,
+                                          None, ns)
+        elif kernel == "tc":
             native.pooled_attention_tc(o, qd, kp, vp, pkp if pool else None, pvp if pool else None, table,
                                        ptable if pool else None, page, pos, _i32([0, n]), 1, H, scale, window, pool, sink,
                                        mixd, None)
@@ -490,6 +504,8 @@ def test_single_keys_at_the_windows_edge_and_in_pooled_blocks(window, pool, dtyp
         cut_sets.append([needle + 1] + [1] * (first - needle + 3) + [T])
     for cuts in cut_sets:
       for kernel in _kernels(H, G, dk, dv, dtype):
+        if kernel in ("split3", "split7") and len(cuts) > 20:
+            continue
         got = _run_pooled_attention(q, k, v, 1.0, window, pool, dtype, page, cuts, kernel=kernel)
         what = f"{kernel}, window {window}, pool {pool}, cuts {cuts[:4]}"
         for i in range(T):
