@@ -454,8 +454,11 @@ pooled_attention_split_kernel(float* __restrict__ part, const T* __restrict__ q,
   }
 }
 
-// A CTA per (token, kv head c): f[split][g] = exp(m_split,g - M_g) / L_g; V[g][:] = sum_split f U_split[g][c][:] to shared
-// memory (every load coalesced); then out[t][h][:] = sum_g mix[h][g] V[g][:] for the heads h of c's group.
+// A CTA per (token, kv head c, 32 value columns): f[split][g] = exp(m_split,g - M_g) / L_g; V[g][:] = sum_split f
+// U_split[g][c][:] to shared memory (every load coalesced, the shares' loads of a thread on their way together); then
+// out[t][h][:] = sum_g mix[h][g] V[g][:] for the heads h of c's group.
+constexpr int kPaMergeCols = 32;
+
 template <typename T>
 __global__ void pooled_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
                                               const int* __restrict__ seq_of_token, int H, int G, int dv, int nsplit,
@@ -463,12 +466,13 @@ __global__ void pooled_attention_merge_kernel(T* __restrict__ out, const float* 
                                               int64_t ldg) {
   atom::pdl_trigger();
   atom::pdl_wait();
-  const int t = blockIdx.x, c = blockIdx.y;
+  const int t = blockIdx.x, c = blockIdx.y, j0 = blockIdx.z * kPaMergeCols;
   if (seq_of_token[t] < 0) return;
-  extern __shared__ float f_s[];              // [nsplit][H], then mix [H][H], then V [H][dv]
+  extern __shared__ float f_s[];              // [nsplit][H], then mix [H][H], then V [H][32]
   float* mix_s = f_s + nsplit * H;
   float* V_s = mix_s + H * H;
   const int n_out = H * G * dv, per = H / G;
+  const int nj = min(kPaMergeCols, dv - j0);
   const int64_t stride = 2 * H + n_out;
   const float* pt = part + (int64_t)t * nsplit * stride;
   for (int g = threadIdx.x; g < H; g += blockDim.x) {
@@ -486,24 +490,29 @@ __global__ void pooled_attention_merge_kernel(T* __restrict__ out, const float* 
   }
   for (int e = threadIdx.x; e < H * H; e += blockDim.x) mix_s[e] = mix ? mix[e] : ((e / H == e % H) ? 1.f : 0.f);
   __syncthreads();
-  for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
-    const int g = e / dv, jj = e - g * dv;
-    const float* u = pt + 2 * H + (g * G + c) * dv + jj;
-    float a0 = 0.f, a1 = 0.f;
-    int sp = 0;
-    for (; sp + 1 < nsplit; sp += 2) {
-      a0 = fmaf(f_s[sp * H + g], u[sp * stride], a0);
-      a1 = fmaf(f_s[(sp + 1) * H + g], u[(sp + 1) * stride], a1);
+  for (int e = threadIdx.x; e < H * kPaMergeCols; e += blockDim.x) {
+    const int g = e / kPaMergeCols, jj = e - g * kPaMergeCols;
+    float a = 0.f;
+    if (jj < nj) {
+      const float* u = pt + 2 * H + (g * G + c) * dv + j0 + jj;
+      for (int sp0 = 0; sp0 < nsplit; sp0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = sp0 + k < nsplit ? u[(sp0 + k) * stride] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (sp0 + k < nsplit) a = fmaf(f_s[(sp0 + k) * H + g], v[k], a);
+      }
     }
-    if (sp < nsplit) a0 = fmaf(f_s[sp * H + g], u[sp * stride], a0);
-    V_s[e] = a0 + a1;
+    V_s[e] = a;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < per * dv; e += blockDim.x) {
-    const int h = c * per + e / dv, jj = e % dv;
+  for (int e = threadIdx.x; e < per * kPaMergeCols; e += blockDim.x) {
+    const int h = c * per + e / kPaMergeCols, jj = e % kPaMergeCols;
+    if (jj >= nj) continue;
     float o = 0.f;
-    for (int g = 0; g < H; ++g) o = fmaf(mix_s[h * H + g], V_s[g * dv + jj], o);
-    const int col = h * dv + jj;
+    for (int g = 0; g < H; ++g) o = fmaf(mix_s[h * H + g], V_s[g * kPaMergeCols + jj], o);
+    const int col = h * dv + j0 + jj;
     if (gate) o = o / (1.f + expf(-to_float(gate[(int64_t)t * ldg + col])));
     out[(int64_t)t * H * dv + col] = from_float<T>(o);
   }
@@ -569,10 +578,10 @@ ATOM_EXPORT int atom_pooled_attention_split(void* out, float* part, const void* 
   a.chunk = atom::pa_split_chunk(H, G, dk, dv);
   a.scale = scale; a.sink = sink; a.mix = mix; a.ldq = ldq; a.ldg = ldg;
   const size_t smem = atom::pa_split_smem_bytes(H, G, dk, dv, a.chunk);
-  const size_t msmem = sizeof(float) * ((size_t)nsplit * H + (size_t)H * H + (size_t)H * dv);
-  const int mthreads = H * dv >= 256 ? 256 : 128;
+  const size_t msmem = sizeof(float) * ((size_t)nsplit * H + (size_t)H * H + (size_t)H * atom::kPaMergeCols);
+  const int mthreads = H * atom::kPaMergeCols >= 256 ? 256 : 128;
   if (msmem > 48 * 1024) return ATOM_ERR_ARG;
-  const dim3 grid(T, nsplit), mgrid(T, G);
+  const dim3 grid(T, nsplit), mgrid(T, G, (dv + atom::kPaMergeCols - 1) / atom::kPaMergeCols);
 #define ATOM_PA_SPLIT(TT, HP)                                                                                         \
   {                                                                                                                   \
     auto kern = atom::pooled_attention_split_kernel<TT, HP>;                                                          \

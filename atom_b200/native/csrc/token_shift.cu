@@ -39,6 +39,52 @@ __global__ void token_shift_mix_kernel(T* __restrict__ out, const T* __restrict_
   }
 }
 
+// bfloat16 rows of a multiple of 8 numbers: a thread owns 8 columns in a row, every array moves 16 bytes at a time.
+__global__ void token_shift_mix_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ h,
+                                                const void* __restrict__ mu, int mu_dtype, __nv_bfloat16* __restrict__ state,
+                                                const int* __restrict__ seq_of_token, const int* __restrict__ cu_q,
+                                                const int* __restrict__ state_slots, int Tn, int W, int n_mix,
+                                                int write_state) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int t = blockIdx.x;
+  const int s = seq_of_token[t];
+  if (s < 0) return;
+  const int first = cu_q[s], last = cu_q[s + 1] - 1;
+  const bool head = (t == first);
+  __nv_bfloat16* srow = state + (int64_t)state_slots[s] * W;
+  const __nv_bfloat16* cur_row = h + (int64_t)t * W;
+  const __nv_bfloat16* prev_row = head ? srow : h + (int64_t)(t - 1) * W;
+  const __nv_bfloat16* last_row = h + (int64_t)last * W;
+  for (int i = threadIdx.x * 8; i < W; i += blockDim.x * 8) {
+    const uint4 cq = *reinterpret_cast<const uint4*>(cur_row + i);
+    const uint4 pq = *reinterpret_cast<const uint4*>(prev_row + i);
+    if (head && write_state) *reinterpret_cast<uint4*>(srow + i) = *reinterpret_cast<const uint4*>(last_row + i);
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cq);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&pq);
+    float cur[8], d[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(c2[e]), b = __bfloat1622float2(p2[e]);
+      cur[2 * e] = a.x;
+      cur[2 * e + 1] = a.y;
+      d[2 * e] = b.x - a.x;
+      d[2 * e + 1] = b.y - a.y;
+    }
+    for (int m = 0; m < n_mix; ++m) {
+      uint4 oq;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oq);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float w0 = load_as_float(mu, mu_dtype, (int64_t)m * W + i + 2 * e);
+        const float w1 = load_as_float(mu, mu_dtype, (int64_t)m * W + i + 2 * e + 1);
+        o2[e] = __floats2bfloat162_rn(fmaf(d[2 * e], w0, cur[2 * e]), fmaf(d[2 * e + 1], w1, cur[2 * e + 1]));
+      }
+      *reinterpret_cast<uint4*>(out + ((int64_t)m * Tn + t) * W + i) = oq;
+    }
+  }
+}
+
 }  // namespace atom
 
 // out: [n_mix, T, W]; h: [T, W]; mu: [n_mix, W]; state: [slots, W] of the activation type.
@@ -52,6 +98,12 @@ ATOM_EXPORT int atom_token_shift_mix(void* out, const void* h, int dtype, const 
     atom::launch_pdl(atom::token_shift_mix_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)out,
                      (const float*)h, mu, mu_dtype, (float*)state, seq_of_token, cu_q, state_slots, T, W, n_mix,
                      write_state);
+  } else if (dtype == ATOM_BF16 && W % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)h % 16) == 0 &&
+             ((uintptr_t)state % 16) == 0) {
+    const int vt = W / 8 >= 256 ? 256 : (W / 8 >= 128 ? 128 : (W / 8 >= 64 ? 64 : 32));
+    atom::launch_pdl(atom::token_shift_mix_bf16_vec_kernel, dim3(T), dim3(vt), 0, stream, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)h, mu, mu_dtype, (__nv_bfloat16*)state, seq_of_token, cu_q, state_slots, T, W,
+                     n_mix, write_state);
   } else if (dtype == ATOM_BF16) {
     atom::launch_pdl(atom::token_shift_mix_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
                      (__nv_bfloat16*)out, (const __nv_bfloat16*)h, mu, mu_dtype, (__nv_bfloat16*)state, seq_of_token,
