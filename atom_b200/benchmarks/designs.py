@@ -100,11 +100,11 @@ def kibotar_config(width: int, heads: int, layers: int) -> dict:
                      "rot": {"base": 1000000.0, "dims": 128,
                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
                      "mask": {"size": 1024, "pool": 64}}}
-    gla = {"type": "gla", "mlp": dense, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 64}}
+    gla = {"type": "gla", "mlp": dense, "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 8.0, "rank": 64}}
     kinds = [lat, att, gla]
     unique = max(2, layers - 1)          # the second layer runs twice: ``layers`` layer runs in all
     return {"architecture": "Kibotar", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
-            "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 127, "mul_cur": 7}},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 257, "mul_cur": 11}},
             "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [kinds[i % 3] for i in range(unique)]}
 
 

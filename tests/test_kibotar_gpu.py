@@ -69,7 +69,7 @@ def test_token_shift_carries_the_last_row_from_step_to_step(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("buckets,mul_prev,mul_cur", [(53, 31, 5), (1, 9, 4), (1021, 1 << 40, 999983), (7, 0, 1)])
+@pytest.mark.parametrize("buckets,mul_prev,mul_cur", [(53, 31, 5), (1, 9, 4), (1019, 1 << 40, 999983), (7, 0, 1)])
 def test_pair_embedding_remembers_the_previous_token(dtype, buckets, mul_prev, mul_cur):
     """The row of the pair table depends on the token before, also across steps and after the slot held another
     request; a request's first token takes the table's last row."""
@@ -115,7 +115,7 @@ def test_pair_embedding_remembers_the_previous_token(dtype, buckets, mul_prev, m
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("W", [44, 192, 1000])
+@pytest.mark.parametrize("W", [44, 200, 1000])
 def test_norm_after_a_sub_block_fused_with_the_next_norm(dtype, W):
     """residual += rmsnorm(delta; w1); out = rmsnorm(residual; w2) in one kernel, also on picked rows."""
     from atom_b200 import native
@@ -149,7 +149,7 @@ GLA_CASES = [  # H, dk, dv, tau, rank, lens
     (4, 4, 8, 32.0, 1, (33, 64, 65)),
     (2, 64, 64, 16.0, 16, (300, 40, 131)),
     (2, 128, 96, 16.0, 8, (130, 3, 70)),
-    (6, 32, 32, 16.0, 16, (2100, 7, 200)),
+    (5, 32, 48, 12.0, 12, (2100, 7, 200)),
 ]
 
 
@@ -223,7 +223,7 @@ LAT_CASES = [  # H, dn, dv, R, lens, page
     (3, 8, 12, 64, (70, 9, 41), 16),
     (2, 16, 8, 64, (37, 5, 18), 8),
     (1, 28, 12, 24, (50, 2, 31), 16),
-    (6, 32, 80, 128, (300, 40, 131), 16),
+    (6, 48, 64, 128, (300, 40, 131), 16),
     (4, 64, 32, 128, (130, 3, 70), 32),
 ]
 
@@ -281,7 +281,7 @@ ATT_CASES = [  # H, G, dk, dv, (base, dims, scaling), (window, pool), page, lens
     (5, 5, 20, 12, (1000.0, 12, None), (1, 2), 16, (33, 5, 20)),
     (6, 1, 12, 28, None, (5, 16), 16, (90, 48, 7)),
     (2, 2, 16, 16, (10000.0, 16, None), (33, None), 8, (64, 65, 63)),
-    (8, 2, 64, 64, (1000000.0, 64, (4.0, 1.0, 4.0, 1024)), (136, 16), 16, (400, 40, 153)),
+    (8, 2, 64, 48, (200000.0, 32, (8.0, 1.0, 2.0, 512)), (120, 24), 16, (400, 40, 153)),
     (8, 4, 128, 128, (100000.0, 32, None), (50, 8), 32, (140, 60, 10)),
     (16, 4, 32, 64, (10000.0, 32, None), (17, 16), 16, (64, 33, 3)),
 ]
@@ -473,7 +473,7 @@ def _plain_weights(q, k, v, scale, window, pool, sink=True, mix=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window,pool", [(1, 1), (2, 3), (16, 4), (17, 16), (40, 8), (64, 64), (136, 16), (300, 7), (5, 32)])
+@pytest.mark.parametrize("window,pool", [(1, 1), (2, 3), (16, 4), (17, 16), (40, 8), (64, 64), (120, 24), (300, 7), (5, 32)])
 def test_single_keys_at_the_windows_edge_and_in_pooled_blocks(window, pool, dtype):
     """One key row in the middle of the request carries a mark that only it has and a score far above all others.  It is
     seen as a token at distance window - 1 and not at distance window; from the position at which its block lies wholly
@@ -565,7 +565,7 @@ def test_far_block_among_hundreds(dtype):
 
 
 TC_CASES = [  # H, G, dk, dv, window, pool, page, T, talk
-    (4, 2, 16, 32, 24, 4, 16, 200, True), (8, 2, 64, 64, 136, 16, 16, 333, True), (6, 3, 80, 48, 90, 7, 16, 300, True),
+    (4, 2, 16, 32, 24, 4, 16, 200, True), (8, 2, 64, 48, 120, 24, 16, 333, True), (6, 3, 80, 48, 90, 7, 16, 300, True),
     (4, 1, 128, 128, 0, 0, 16, 270, False), (2, 2, 256, 16, 65, 64, 8, 200, True), (3, 1, 48, 112, 1, 1, 16, 150, True),
     (5, 5, 32, 80, 200, 0, 64, 520, False), (16, 4, 128, 128, 100, 32, 16, 600, True), (16, 8, 32, 32, 17, 16, 16, 210, True),
 ]
@@ -663,7 +663,7 @@ def test_every_cut_matches_plain(dirs, name, dtype):
     tokens in a pool so small that pages and state slots are used again."""
     seqs = _seqs(name)
     ref = _plain_logits(dirs[name], seqs)
-    budget = 448 if name == "D" else 320
+    budget = 512 if name == "D" else 320
     mixed, peak = traces.mixed(seqs, max_live=4, budget_tokens=budget)
     assert peak <= budget < sum(-(-len(t) // 64) * 64 for t in seqs.values())
     runner = _runner(dirs[name], dtype, budget, tk.PAGE[name], max_num_seqs=4)

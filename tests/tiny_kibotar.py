@@ -74,11 +74,11 @@ CONFIGS: Dict[str, dict] = {
                      _lat(1, 28, 12, 24, 0.25, _dense(60)),
                      _att(2, 2, 16, 16, 0.4, rot=(10000.0, 16), mask=(33, None), mlp=_dense(44)),
                      _gla(4, 4, 8, 32.0, 1)]},
-    "D": {"architecture": "Kibotar", "vocab": 512, "width": 128, "norm": {"eps": 1e-5}, "embedding": _emb(0.5, 251, 64, 3),
+    "D": {"architecture": "Kibotar", "vocab": 512, "width": 128, "norm": {"eps": 1e-5}, "embedding": _emb(0.6, 251, 64, 3),
           "loop": {"start": 2, "stop": 3, "times": 1},
-          "layers": [_att(8, 2, 64, 64, 0.2, rot=(100000.0, 32, (4.0, 1.0, 4.0, 256)), mask=(128, 32), mlp=_dense(256)),
-                     _gla(2, 64, 64, 16.0, 16, _dense(256)),
-                     _lat(4, 64, 32, 128, 0.15, _dense(256))]},
+          "layers": [_att(8, 4, 64, 32, 0.2, rot=(100000.0, 32, (8.0, 1.0, 2.0, 256)), mask=(128, 32), mlp=_dense(320)),
+                     _gla(2, 64, 64, 12.0, 16, _dense(320)),
+                     _lat(4, 64, 32, 128, 0.15, _dense(320))]},
 }
 SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14}
 PAGE = {"A": 16, "B": 8, "C": 16, "D": 32}
